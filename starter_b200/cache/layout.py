@@ -22,11 +22,17 @@ def pages_for(tokens: int) -> int:
 
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values per token: ``num_kv_heads * head_dim`` each; ``window`` None = keep all."""
+    """Keys and values per token: ``num_kv_heads`` rows of ``head_dim`` keys and of ``value_dim``
+    values (None: as many as keys); ``window`` None = keep all."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+
+    @property
+    def value_size(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)

@@ -61,7 +61,7 @@ class SequenceCache:
             need: KVNeed = group.need
             shape = (len(group.entries), self.num_pages, need.num_kv_heads, PAGE_TOKENS, need.head_dim)
             self.keys.append(torch.zeros(shape, dtype=dtype, device=self.device))
-            self.values.append(torch.zeros(shape, dtype=dtype, device=self.device))
+            self.values.append(torch.zeros(shape[:-1] + (need.value_size,), dtype=dtype, device=self.device))
             for i, entry in enumerate(group.entries):
                 self._where[entry] = (g, i)
         self.state = {}
@@ -75,7 +75,8 @@ class SequenceCache:
     # ------------------------------------------------------------------ storage views
 
     def entry_pages(self, entry: int):
-        """``(keys, values)`` of one cache entry, each ``[pages, kv_heads, 64, head_dim]``."""
+        """``(keys, values)`` of one cache entry: ``[pages, kv_heads, 64, head_dim]`` and
+        ``[pages, kv_heads, 64, value_dim]`` (the same shape unless the entry's need says otherwise)."""
         g, i = self._where[entry]
         return self.keys[g][i], self.values[g][i]
 
@@ -88,7 +89,8 @@ class SequenceCache:
     def bytes_per_token(self) -> int:
         total = 0
         for group in self.groups:
-            total += 2 * len(group.entries) * group.need.num_kv_heads * group.need.head_dim * self.dtype.itemsize
+            total += (len(group.entries) * group.need.num_kv_heads * (group.need.head_dim + group.need.value_size)
+                      * self.dtype.itemsize)
         return total
 
     # ------------------------------------------------------------------ sequences

@@ -1,14 +1,20 @@
+from .goguvik import GoguvikConfig
 from .qwen3 import ConfigError, Qwen3Config
 from .registry import ARCHITECTURES, config_from_dict, load_config, register_architecture
 from .spec import (
     AttentionSpec,
+    DifferentialAttentionSpec,
+    DynamicTanhSpec,
     GatedFeedForwardSpec,
+    HyperConnectionSpec,
     LayerSpec,
     ModelSpec,
     NormSpec,
+    QueryTemperatureSpec,
     RopeSpec,
     ScheduleEntry,
     default_schedule,
+    hyper_layer,
     prenorm_layer,
 )
 
@@ -16,7 +22,13 @@ __all__ = [
     "ARCHITECTURES",
     "AttentionSpec",
     "ConfigError",
+    "DifferentialAttentionSpec",
+    "DynamicTanhSpec",
     "GatedFeedForwardSpec",
+    "GoguvikConfig",
+    "HyperConnectionSpec",
+    "QueryTemperatureSpec",
+    "hyper_layer",
     "LayerSpec",
     "ModelSpec",
     "NormSpec",

@@ -10,6 +10,7 @@ from __future__ import annotations
 import json
 import os
 
+from .goguvik import GoguvikConfig
 from .qwen3 import ConfigError, Qwen3Config
 
 ARCHITECTURES: dict = {}
@@ -23,13 +24,24 @@ def register_architecture(name: str, config_cls) -> None:
 
 
 register_architecture(Qwen3Config.architecture, Qwen3Config)
+register_architecture(GoguvikConfig.architecture, GoguvikConfig)
+
+
+def architecture_name(raw: dict):
+    """The architecture a config.json names: the first of ``architectures``, or ``architecture``."""
+    names = raw.get("architectures")
+    if isinstance(names, (list, tuple)) and names:
+        return names[0]
+    if isinstance(names, str) and names:
+        return names
+    name = raw.get("architecture")
+    return name if isinstance(name, str) and name else None
 
 
 def config_from_dict(raw: dict):
-    names = raw.get("architectures")
-    if not names:
+    name = architecture_name(raw)
+    if name is None:
         raise ConfigError("config.json lacks required key(s): architectures")
-    name = names[0]
     if name not in ARCHITECTURES:
         raise ConfigError(
             f"unknown architecture {name!r}; known: " + ", ".join(sorted(ARCHITECTURES))

@@ -26,6 +26,15 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class DynamicTanhSpec:
+    """Dynamic Tanh in a norm's place: ``tanh(alpha * x) * weight + bias`` with a scalar ``alpha``; it
+    computes no mean and no variance."""
+
+    size: int
+    kind: str = "dynamic_tanh"
+
+
+@dataclass(frozen=True)
 class RopeSpec:
     """Half-split rotary position encoding over the whole head."""
 
@@ -52,6 +61,54 @@ class AttentionSpec:
     position: Optional[RopeSpec]
     window: Optional[int] = None
     kind: str = "attention"
+
+
+@dataclass(frozen=True)
+class QueryTemperatureSpec:
+    """Queries at position ``p`` are multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``."""
+
+    coef: float
+    every: int
+
+
+@dataclass(frozen=True)
+class DifferentialAttentionSpec:
+    """Causal grouped-query attention with two softmax maps per head over the same values.
+
+    A query head has two query vectors of ``head_dim`` each and a key/value head two key vectors and
+    one value vector of ``value_dim``; the head's output is ``a1 - lambda * a2`` with ``lambda =
+    exp(lq1 . lk1) - exp(lq2 . lk2) + lambda_init`` (four learnt vectors of ``head_dim``), divided by
+    its root mean square over ``value_dim`` (``norm_eps`` inside the root, no gain) and multiplied by
+    ``1 - lambda_init``.  ``bias``: q, k, v and the output projection have biases.  ``gated``: the
+    concatenated heads are multiplied by ``sigmoid(g(x))`` before the output projection.
+    ``own_kv`` false: the layer has no key and value projections and attends over the cache entry
+    another layer fills (the run order says which).  No rotation; ``q_temperature`` or None.
+    """
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    lambda_init: float
+    norm_eps: float
+    q_temperature: Optional[QueryTemperatureSpec] = None
+    bias: bool = True
+    gated: bool = True
+    own_kv: bool = True
+    window: Optional[int] = None
+    position: Optional[RopeSpec] = None
+    kind: str = "differential_attention"
+
+
+@dataclass(frozen=True)
+class HyperConnectionSpec:
+    """How one sublayer reads from and writes to ``streams`` residual streams: ``in`` and ``out``
+    vectors of that length and a ``[from, to]`` mixing matrix."""
+
+    streams: int
+    kind: str = "hyper"
 
 
 @dataclass(frozen=True)
@@ -85,6 +142,15 @@ class LayerSpec:
         if name in parts:
             return parts[name]
         raise AttributeError(f"this layer has no part named {name!r} (it has: {', '.join(parts)})")
+
+
+def hyper_layer(mixer, feed_forward, norm1, norm2, connection, names) -> LayerSpec:
+    """The pre-norm layer over several residual streams; ``feed_forward`` (and ``norm2``) None: the
+    layer is its mixer alone."""
+    if feed_forward is None:
+        return LayerSpec({"mixer": mixer, "norm1": norm1, "connection1": connection}, names, "hyper_mixer_only")
+    return LayerSpec({"mixer": mixer, "feed_forward": feed_forward, "norm1": norm1, "norm2": norm2,
+                      "connection1": connection, "connection2": connection}, names, "hyper_prenorm")
 
 
 def prenorm_layer(mixer, feed_forward, norm1, norm2, names, arrangement: str = "prenorm") -> LayerSpec:
@@ -124,6 +190,14 @@ class ModelSpec:
     lm_head_name: str
     max_position: int = 0
     extra: dict = field(default_factory=dict)
+    #: how many residual streams a token has (1: the single stream of the working type; more: float32
+    #: streams that the layers' hyper-connections read and write, summed before the final norm)
+    streams: int = 1
+    #: the parameters of the final norm by logical name -> checkpoint name (None: its one ``weight``
+    #: under ``final_norm_name``)
+    final_norm_names: Optional[dict] = None
+    #: checkpoint tensors that may be there and are not read
+    ignored_tensors: tuple = ()
 
     def cache_entries(self) -> int:
         return 1 + max((e.cache for e in self.schedule), default=-1)

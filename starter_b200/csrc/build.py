@@ -45,6 +45,8 @@ SOURCES = (
     "gemm_prompt_tcgen05",
     "dense_chain",
     "sampling",
+    "streams",
+    "attention_diff",
 )
 
 _lock = threading.Lock()

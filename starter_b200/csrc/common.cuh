@@ -43,6 +43,21 @@ __device__ __forceinline__ uint32_t pack_exact_bf16(float lo, float hi) {
   return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u);
 }
 
+// The activation of a gated feed-forward, chosen by the code the entry points take as `gated`:
+// 1: silu, g * sigmoid(g); 2: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))),
+// which equals g * sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3)).  The fast forms (a few float ulp off) are
+// for results that are rounded to bfloat16 at once; the 32-bit path uses the exact ones.
+#define SB_ACT_SILU 1
+#define SB_ACT_GELU_TANH 2
+__device__ __forceinline__ float gate_act_fast(float g, int act) {
+  const float z = act == SB_ACT_GELU_TANH ? -1.5957691216057308f * (g + 0.044715f * g * g * g) : -g;
+  return __fdividef(g, 1.f + __expf(z));
+}
+__device__ __forceinline__ float gate_act(float g, int act) {
+  if (act == SB_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.f + expf(-g));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

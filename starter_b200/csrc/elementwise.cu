@@ -298,7 +298,7 @@ static int launch_rmsnorm(void* x, const void* delta, const void* gain, void* y,
 
 // act[r, c] = round(silu(gate)) * up with gate = gu[r, c], up = gu[r, inner + c].
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total, int kind) {
   pdl_trigger();
   pdl_wait();
   SB_BEHIND_WAIT(gu);
@@ -309,14 +309,14 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
     const int col = (int)(i - row * inner);
     const float g = to_f<T>(gu[row * 2 * inner + col]);
     const float u = to_f<T>(gu[row * 2 * inner + inner + col]);
-    const float silu = rnd<T>(g / (1.f + expf(-g)));
+    const float silu = rnd<T>(gate_act(g, kind));
     act[i] = from_f<T>(silu * u);
   }
 }
 
 // The same with 16-byte accesses: N consecutive columns per thread (inner % N == 0, aligned rows).
 template <typename T>
-__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t groups) {
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t groups, int kind) {
   constexpr int N = 16 / sizeof(T);
   pdl_trigger();
   pdl_wait();
@@ -334,8 +334,14 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act,
     for (int j = 0; j < N; j += 2) {
       // the result is rounded to 8 bits of mantissa: the fast exponential and quotient (a few
       // float ulp, as in the product kernel's gated epilogue) do not show; float keeps the exact ones
-      float s0 = sizeof(T) == 2 ? __fdividef(g[j], 1.f + __expf(-g[j])) : g[j] / (1.f + expf(-g[j]));
-      float s1 = sizeof(T) == 2 ? __fdividef(g[j + 1], 1.f + __expf(-g[j + 1])) : g[j + 1] / (1.f + expf(-g[j + 1]));
+      float s0, s1;
+      if (kind == SB_ACT_GELU_TANH) {
+        s0 = sizeof(T) == 2 ? gate_act_fast(g[j], kind) : gate_act(g[j], kind);
+        s1 = sizeof(T) == 2 ? gate_act_fast(g[j + 1], kind) : gate_act(g[j + 1], kind);
+      } else {
+        s0 = sizeof(T) == 2 ? __fdividef(g[j], 1.f + __expf(-g[j])) : g[j] / (1.f + expf(-g[j]));
+        s1 = sizeof(T) == 2 ? __fdividef(g[j + 1], 1.f + __expf(-g[j + 1])) : g[j + 1] / (1.f + expf(-g[j + 1]));
+      }
       rnd2<T>(s0, s1);
       o[j] = s0 * u[j];
       o[j + 1] = s1 * u[j + 1];
@@ -375,7 +381,7 @@ int sb_rmsnorm(int dtype, int gain_dtype, void* x, const void* delta, const void
   return -1;
 }
 
-int sb_swiglu(int dtype, const void* gu, void* act, int n_rows, int inner, cudaStream_t s) {
+int sb_swiglu(int dtype, const void* gu, void* act, int n_rows, int inner, int kind, cudaStream_t s) {
   const size_t total = (size_t)n_rows * inner;
   if (total == 0) return 0;
   const int threads = 256;
@@ -385,14 +391,14 @@ int sb_swiglu(int dtype, const void* gu, void* act, int n_rows, int inner, cudaS
     size_t vblocks = (groups + threads - 1) / threads;
     if (vblocks > 148 * 32) vblocks = 148 * 32;
     if (dtype == 0)
-      return launch_dependent(swiglu_vec_kernel<float>, dim3((int)vblocks), dim3(threads), 0, s, (const float*)gu, (float*)act, inner, groups);
-    return launch_dependent(swiglu_vec_kernel<bf16>, dim3((int)vblocks), dim3(threads), 0, s, (const bf16*)gu, (bf16*)act, inner, groups);
+      return launch_dependent(swiglu_vec_kernel<float>, dim3((int)vblocks), dim3(threads), 0, s, (const float*)gu, (float*)act, inner, groups, kind);
+    return launch_dependent(swiglu_vec_kernel<bf16>, dim3((int)vblocks), dim3(threads), 0, s, (const bf16*)gu, (bf16*)act, inner, groups, kind);
   }
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == 0)
-    return launch_dependent(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, (float*)act, inner, total);
-  return launch_dependent(swiglu_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, s, (const bf16*)gu, (bf16*)act, inner, total);
+    return launch_dependent(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, (float*)act, inner, total, kind);
+  return launch_dependent(swiglu_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, s, (const bf16*)gu, (bf16*)act, inner, total, kind);
 }
 
 }  // extern "C"

@@ -310,7 +310,7 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float gr = rnd<bf16>(v[j]), ur = rnd<bf16>(u[j]);
-            v[j] = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
+            v[j] = rnd<bf16>(args.gated == SB_ACT_GELU_TANH ? gate_act_fast(gr, SB_ACT_GELU_TANH) : gr / (1.f + __expf(-gr))) * ur;
           }
         }
         if (c == n_chunks - 1) {

@@ -268,7 +268,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float gr = rnd<bf16>(g[j]), ur = rnd<bf16>(u[j]);
-            g[j] = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
+            g[j] = rnd<bf16>(args.gated == SB_ACT_GELU_TANH ? gate_act_fast(gr, SB_ACT_GELU_TANH) : gr / (1.f + __expf(-gr))) * ur;
           }
         }
         const int ncol = (GATED ? tile * 64 : tile * TILE_N) + orow;

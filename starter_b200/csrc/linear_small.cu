@@ -24,7 +24,7 @@ __device__ __forceinline__ void load_vec(const T* p, float* out) {
 
 template <typename T, typename O, int MB, int VEC, bool GATED>
 __global__ void linear_small_kernel(const T* __restrict__ x, const T* __restrict__ w,
-                                    O* __restrict__ y, int rows, int n_out, int k_dim) {
+                                    O* __restrict__ y, int rows, int n_out, int k_dim, int act) {
   const int lane = threadIdx.x & 31;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int n_warps = (gridDim.x * blockDim.x) >> 5;
@@ -61,7 +61,7 @@ __global__ void linear_small_kernel(const T* __restrict__ x, const T* __restrict
           if (GATED) {
             // gate and up are the two projection outputs, each rounded to the working type first
             const float g = rnd<T>(v), u = rnd<T>(v2);
-            v = rnd<T>(g / (1.f + expf(-g))) * u;
+            v = rnd<T>(gate_act(g, act)) * u;
           }
           y[(size_t)(m0 + m) * n_out + n] = from_f<O>(v);
         }
@@ -71,7 +71,7 @@ __global__ void linear_small_kernel(const T* __restrict__ x, const T* __restrict
 }
 
 template <typename T, typename O, bool GATED>
-static int launch(const void* x, const void* w, void* y, int rows, int n_out, int k_dim,
+static int launch(const void* x, const void* w, void* y, int rows, int n_out, int k_dim, int act,
                   cudaStream_t s) {
   if (rows == 0 || n_out == 0) return 0;
   const int threads = 256;
@@ -82,7 +82,7 @@ static int launch(const void* x, const void* w, void* y, int rows, int n_out, in
   const T* xp = (const T*)x;
   const T* wp = (const T*)w;
   O* yp = (O*)y;
-#define GO(MB, VEC) linear_small_kernel<T, O, MB, VEC, GATED><<<blocks, threads, 0, s>>>(xp, wp, yp, rows, n_out, k_dim)
+#define GO(MB, VEC) linear_small_kernel<T, O, MB, VEC, GATED><<<blocks, threads, 0, s>>>(xp, wp, yp, rows, n_out, k_dim, act)
   if (vec_ok) {
     constexpr int V = sizeof(T) == 2 ? 8 : 4;
     if (rows == 1) GO(1, V);
@@ -101,19 +101,20 @@ static int launch(const void* x, const void* w, void* y, int rows, int n_out, in
 extern "C" {
 
 // dtype: 0 float, 1 bfloat16 (x and w).  out_float != 0 writes y as float whatever dtype is.
-// gated != 0: w is [2 * n_out, k_dim] and y[m, n] = round(silu(x.w[n])) * (x.w[n + n_out]).
+// gated != 0: w is [2 * n_out, k_dim] and y[m, n] = round(act(x.w[n])) * (x.w[n + n_out]), act by the
+// code in `gated` (1 silu, 2 tanh-gelu).
 int sb_linear_small(int dtype, int out_float, int gated, const void* x, const void* w, void* y,
                     int rows, int n_out, int k_dim, cudaStream_t s) {
   if (dtype == 0) {
-    return gated ? launch<float, float, true>(x, w, y, rows, n_out, k_dim, s)
-                 : launch<float, float, false>(x, w, y, rows, n_out, k_dim, s);
+    return gated ? launch<float, float, true>(x, w, y, rows, n_out, k_dim, gated, s)
+                 : launch<float, float, false>(x, w, y, rows, n_out, k_dim, gated, s);
   }
   if (out_float) {
     if (gated) return -1;
-    return launch<bf16, float, false>(x, w, y, rows, n_out, k_dim, s);
+    return launch<bf16, float, false>(x, w, y, rows, n_out, k_dim, gated, s);
   }
-  return gated ? launch<bf16, bf16, true>(x, w, y, rows, n_out, k_dim, s)
-               : launch<bf16, bf16, false>(x, w, y, rows, n_out, k_dim, s);
+  return gated ? launch<bf16, bf16, true>(x, w, y, rows, n_out, k_dim, gated, s)
+               : launch<bf16, bf16, false>(x, w, y, rows, n_out, k_dim, gated, s);
 }
 
 }  // extern "C"

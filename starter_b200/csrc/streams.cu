@@ -1,0 +1,205 @@
+// Several residual streams per token (hyper-connections) and the Dynamic Tanh norm.
+//
+// A model with hyper-connections keeps S copies x_1..x_S of the residual stream per token, as
+// float [tokens][S][hidden] (the residual is a 32-bit sum whatever the working type).  Around a
+// sublayer with the vectors `in` [S], `out` [S] and the matrix `mix` [S][S] (indexed [from][to]):
+//
+//     u    = sum_s in[s] * x_s                       the sublayer's input, before its norm
+//     y    = sublayer(norm(u))
+//     x_t <- sum_s mix[s][t] * x_s + out[t] * y      all t at once, from the old x
+//
+// The update that closes one sublayer and the read that opens the next touch the same S rows, so
+// they are ONE kernel here (as the residual sum and the norm after it are one kernel in the
+// single-stream models): hyper_step applies the pending update of the previous sublayer in place,
+// forms u for the next one and norms it.  With `rows` it does the same for selected rows without
+// writing back, and with in == null it forms the plain sum of the streams: that closes the model.
+//
+// Dynamic Tanh: y = tanh(alpha * x) * w + b with a scalar alpha; no mean, no variance.
+#include "common.cuh"
+
+#define SB_MAX_STREAMS 8
+
+template <typename T>
+__global__ void embed_streams_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                     float* __restrict__ out, int hidden, int vocab, int streams, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(tokens);
+  const int row = blockIdx.x;
+  int tok = tokens[row];
+  const bool bad = tok < 0 || tok >= vocab;
+  if (bad) {
+    if (threadIdx.x == 0 && status) atomicOr(status, 1);
+    tok = 0;
+  }
+  const T* src = table + (size_t)tok * hidden;
+  float* dst = out + (size_t)row * streams * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = bad ? 0.f : to_f<T>(src[c]);
+    for (int s = 0; s < streams; ++s) dst[(size_t)s * hidden + c] = v;
+  }
+}
+
+// norm_kind 0: normed = u (rounded to T); 1: Dynamic Tanh of u.
+template <typename T, int S>
+__global__ void hyper_step_kernel(float* __restrict__ streams, const T* __restrict__ y,
+                                  const float* __restrict__ y_bias, const float* __restrict__ mix_prev,
+                                  const float* __restrict__ out_prev, const float* __restrict__ in_next,
+                                  int norm_kind, const float* __restrict__ alpha_p,
+                                  const float* __restrict__ w, const float* __restrict__ b,
+                                  T* __restrict__ normed, const int* __restrict__ rows, int hidden) {
+  __shared__ float s_mix[S * S], s_out[S], s_in[S];
+  if (threadIdx.x < S * S) s_mix[threadIdx.x] = y ? mix_prev[threadIdx.x] : 0.f;
+  if (threadIdx.x < S) {
+    s_out[threadIdx.x] = y ? out_prev[threadIdx.x] : 0.f;
+    s_in[threadIdx.x] = in_next ? in_next[threadIdx.x] : 1.f;
+  }
+  const float alpha = norm_kind == 1 ? alpha_p[0] : 0.f;
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(y);
+  SB_BEHIND_WAIT(rows);
+  __syncthreads();
+  const int out_row = blockIdx.x;
+  const int in_row = rows ? rows[out_row] : out_row;
+  float* xr = streams + (size_t)in_row * S * hidden;
+  const T* yr = y ? y + (size_t)in_row * hidden : nullptr;
+  T* nr = normed + (size_t)out_row * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float x[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) x[s] = xr[(size_t)s * hidden + c];
+    if (yr) {
+      float yv = to_f<T>(yr[c]);
+      if (y_bias) yv += y_bias[c];
+      float nx[S];
+#pragma unroll
+      for (int t = 0; t < S; ++t) {
+        float a = 0.f;
+#pragma unroll
+        for (int s = 0; s < S; ++s) a += s_mix[s * S + t] * x[s];
+        nx[t] = a + s_out[t] * yv;
+      }
+#pragma unroll
+      for (int t = 0; t < S; ++t) {
+        x[t] = nx[t];
+        if (!rows) xr[(size_t)t * hidden + c] = nx[t];
+      }
+    }
+    float u = 0.f;
+#pragma unroll
+    for (int s = 0; s < S; ++s) u += s_in[s] * x[s];
+    if (norm_kind == 1) u = tanhf(alpha * u) * w[c] + b[c];
+    nr[c] = from_f<T>(u);
+  }
+}
+
+// Dynamic Tanh on a single stream of the working type, with the residual sum in front of it as the
+// RMSNorm kernel has it: with delta, x <- round(x + delta) first (written back unless rows is given).
+template <typename T>
+__global__ void dyt_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ alpha_p,
+                           const float* __restrict__ w, const float* __restrict__ b, T* __restrict__ y,
+                           const int* __restrict__ rows, int hidden) {
+  const float alpha = alpha_p[0];
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(delta);
+  SB_BEHIND_WAIT(rows);
+  const int out_row = blockIdx.x;
+  const int in_row = rows ? rows[out_row] : out_row;
+  T* xr = x + (size_t)in_row * hidden;
+  const T* dr = delta ? delta + (size_t)in_row * hidden : nullptr;
+  T* yr = y + (size_t)out_row * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = to_f<T>(xr[c]);
+    if (dr) {
+      v = rnd<T>(v + to_f<T>(dr[c]));
+      if (!rows) xr[c] = from_f<T>(v);
+    }
+    yr[c] = from_f<T>(tanhf(alpha * v) * w[c] + b[c]);
+  }
+}
+
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ y, const float* __restrict__ bias, int width, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(y);
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) y[i] = from_f<T>(to_f<T>(y[i]) + bias[i % width]);
+}
+
+template <typename T>
+static int launch_step(int S, float* streams, const void* y, const float* y_bias, const float* mix_prev,
+                       const float* out_prev, const float* in_next, int norm_kind, const float* alpha,
+                       const float* w, const float* b, void* normed, const int* rows, int n_rows, int hidden,
+                       cudaStream_t s) {
+  const int threads = hidden >= 1024 ? 256 : 128;
+#define GO(N) case N: return launch_dependent(hyper_step_kernel<T, N>, dim3(n_rows), dim3(threads), 0, s, streams, \
+    (const T*)y, y_bias, mix_prev, out_prev, in_next, norm_kind, alpha, w, b, (T*)normed, rows, hidden)
+  switch (S) {
+    GO(1); GO(2); GO(3); GO(4); GO(5); GO(6); GO(7); GO(8);
+  }
+#undef GO
+  return -2;
+}
+
+extern "C" {
+
+int sb_max_streams() { return SB_MAX_STREAMS; }
+
+// out: float [n_tokens, streams, hidden], every stream the token's embedding.  serial != 0: an
+// ordinary launch (the step's fence, see sb_embedding).
+int sb_embed_streams(int dtype, const int* tokens, const void* table, float* out, int n_tokens, int hidden,
+                     int vocab, int streams, int* status, int serial, cudaStream_t s) {
+  if (n_tokens == 0) return 0;
+  if (streams < 1) return -2;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (serial) {
+    if (dtype == 0)
+      embed_streams_kernel<float><<<n_tokens, threads, 0, s>>>(tokens, (const float*)table, out, hidden, vocab, streams, status);
+    else
+      embed_streams_kernel<bf16><<<n_tokens, threads, 0, s>>>(tokens, (const bf16*)table, out, hidden, vocab, streams, status);
+    return SB_LAUNCH_RESULT();
+  }
+  if (dtype == 0)
+    return launch_dependent(embed_streams_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, tokens, (const float*)table, out, hidden, vocab, streams, status);
+  return launch_dependent(embed_streams_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, tokens, (const bf16*)table, out, hidden, vocab, streams, status);
+}
+
+// streams: float [*, S, hidden].  y (null: no pending update) [*, hidden] of the working type, y_bias
+// null or float [hidden]; mix_prev [S, S] ([from][to]), out_prev [S]; in_next [S] or null (plain sum).
+// normed: [n_rows, hidden] of the working type.  rows null: every row, updated in place; else only
+// those rows and nothing is written back.
+int sb_hyper_step(int dtype, int n_streams, float* streams, const void* y, const float* y_bias,
+                  const float* mix_prev, const float* out_prev, const float* in_next, int norm_kind,
+                  const float* alpha, const float* w, const float* b, void* normed, const int* rows,
+                  int n_rows, int hidden, cudaStream_t s) {
+  if (n_rows == 0) return 0;
+  if (n_streams < 1 || n_streams > SB_MAX_STREAMS) return -2;
+  if (dtype == 0)
+    return launch_step<float>(n_streams, streams, y, y_bias, mix_prev, out_prev, in_next, norm_kind, alpha, w, b, normed, rows, n_rows, hidden, s);
+  return launch_step<bf16>(n_streams, streams, y, y_bias, mix_prev, out_prev, in_next, norm_kind, alpha, w, b, normed, rows, n_rows, hidden, s);
+}
+
+int sb_add_bias(int dtype, void* y, const float* bias, int n_rows, int width, cudaStream_t s) {
+  const size_t total = (size_t)n_rows * width;
+  if (total == 0) return 0;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == 0)
+    return launch_dependent(add_bias_kernel<float>, dim3((int)blocks), dim3(256), 0, s, (float*)y, bias, width, total);
+  return launch_dependent(add_bias_kernel<bf16>, dim3((int)blocks), dim3(256), 0, s, (bf16*)y, bias, width, total);
+}
+
+int sb_dyt(int dtype, void* x, const void* delta, const float* alpha, const float* w, const float* b, void* y,
+           const int* rows, int n_rows, int hidden, cudaStream_t s) {
+  if (n_rows == 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == 0)
+    return launch_dependent(dyt_kernel<float>, dim3(n_rows), dim3(threads), 0, s, (float*)x, (const float*)delta, alpha, w, b, (float*)y, rows, hidden);
+  return launch_dependent(dyt_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, (bf16*)x, (const bf16*)delta, alpha, w, b, (bf16*)y, rows, hidden);
+}
+
+}  // extern "C"

@@ -13,6 +13,7 @@ import torch
 
 from .. import ops
 from ..parts import ParamSpec, lookup
+from ..parts.hyper import close_rows
 
 
 def build_layers(spec, dtype, device):
@@ -58,6 +59,17 @@ def _layer_params(block, names: dict) -> dict:
     return out
 
 
+def _final_norm_params(spec, norm=None) -> dict:
+    """``{checkpoint name: (logical name, ParamSpec)}`` of the final norm."""
+    if norm is None:
+        norm = lookup("norm", spec.final_norm.kind)(spec.final_norm, torch.float32)
+    names = spec.final_norm_names or {"weight": spec.final_norm_name}
+    wanted = norm.param_specs()
+    if set(wanted) != set(names):
+        raise ValueError(f"the final norm has parameters {sorted(wanted)}; the spec names {sorted(names)}")
+    return {names[logical]: (logical, pspec) for logical, pspec in wanted.items()}
+
+
 def expected_tensors(spec) -> dict:
     """``{checkpoint name: ParamSpec}`` in a fixed order: embedding, layers, final norm, head."""
     blocks, _ = build_layers(spec, torch.float32, "cpu")
@@ -65,7 +77,8 @@ def expected_tensors(spec) -> dict:
     for block, layer in zip(blocks, spec.layers):
         for name, (_, _, pspec) in _layer_params(block, layer.names).items():
             out[name] = pspec
-    out[spec.final_norm_name] = ParamSpec((spec.final_norm.size,), "gain")
+    for name, (_, pspec) in _final_norm_params(spec).items():
+        out[name] = pspec
     if not spec.tie_embeddings:
         out[spec.lm_head_name] = ParamSpec((spec.vocab_size, spec.hidden_size))
     return out
@@ -80,6 +93,14 @@ class DecoderModel:
         self.final_norm = lookup("norm", spec.final_norm.kind)(spec.final_norm, dtype)
         self.embed = None
         self.lm_head = None
+        #: True when the layers are arranged over several float32 residual streams (hyper-connections);
+        #: every layer must then be, whatever the number of streams
+        kinds = {hasattr(b, "connection1") for b in self.blocks}
+        if len(kinds) > 1:
+            raise ValueError("layers over several residual streams and layers over one cannot be mixed")
+        self.many_streams = kinds == {True}
+        if not self.many_streams and spec.streams != 1:
+            raise ValueError(f"the spec asks for {spec.streams} residual streams but its layers keep one")
         for entry in spec.schedule:
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"the run order names layer {entry.layer}; the model has {len(self.blocks)}")
@@ -104,7 +125,8 @@ class DecoderModel:
         spec = self.spec
         self.embed = tensors[spec.embed_name]
         self.lm_head = self.embed if spec.tie_embeddings else tensors[spec.lm_head_name]
-        self.final_norm.set_params({"weight": tensors[spec.final_norm_name]})
+        self.final_norm.set_params({logical: tensors[name] for name, (logical, _)
+                                    in _final_norm_params(spec, self.final_norm).items()})
         for block, layer in zip(self.blocks, spec.layers):
             grouped = {}
             wanted = _layer_params(block, layer.names)
@@ -151,7 +173,11 @@ class DecoderModel:
         """Run the layers; returns ``(residual, pending)`` with the last sum still open."""
         # the step's first kernel is an ordinary launch: the fence behind which the step's other
         # kernels may read early what earlier steps left (lengths, cache pages)
-        residual = ops.embedding(ctx.tokens, self.embed, ctx.status, fence=True)
+        if self.many_streams:
+            # several residual streams per token, float32, all equal to the embedding at the start
+            residual = ops.embedding_streams(ctx.tokens, self.embed, self.spec.streams, ctx.status, fence=True)
+        else:
+            residual = ops.embedding(ctx.tokens, self.embed, ctx.status, fence=True)
         ctx.fenced = True
         pending = None
         for entry in self.spec.schedule:
@@ -161,7 +187,10 @@ class DecoderModel:
 
     def logits(self, residual, pending, rows, status=None):
         """Float32 logits ``[len(rows), vocab]`` of the rows asked for."""
-        h = self.final_norm.add_rows(residual, pending, rows)
+        if self.many_streams:
+            h = close_rows(residual, pending, rows, self.final_norm, self.dtype)
+        else:
+            h = self.final_norm.add_rows(residual, pending, rows)
         return ops.linear(h, self.lm_head, out_float=True, status=status)
 
     def forward(self, ctx, rows):

@@ -63,7 +63,8 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0") -> DecoderMode
     spec = config.to_model_spec()
     model = DecoderModel(spec, dtype, device)
     alias = (spec.lm_head_name, spec.embed_name) if spec.tie_embeddings else None
-    tensors = load_checkpoint(model_dir, model.expected_tensors(), dtype, device, tied_alias=alias)
+    tensors = load_checkpoint(model_dir, model.expected_tensors(), dtype, device, tied_alias=alias,
+                              ignored=spec.ignored_tensors)
     model.load_tensors(tensors)
     model.config = config
     return model

@@ -177,15 +177,34 @@ def rmsnorm(x, gain, eps, delta=None, rows=None, out=None):
     return out
 
 
-def swiglu(gate_up):
-    """``round(silu(gate)) * up`` for ``gate_up = [gate | up]`` of shape ``[T, 2 * I]``."""
+#: the activations a gated product knows, and the code the kernels take for each
+ACTIVATIONS = {"silu": 1, "gelu_tanh": 2}
+
+
+def gate_code(gated) -> int:
+    """``gated`` as the kernels' code: False 0, True or ``"silu"`` 1, ``"gelu_tanh"`` 2."""
+    if gated is False or gated is None or gated == 0:
+        return 0
+    if gated is True:
+        return 1
+    if isinstance(gated, int) and gated in ACTIVATIONS.values():
+        return gated
+    try:
+        return ACTIVATIONS[gated]
+    except (KeyError, TypeError):
+        raise KernelError(f"no gated product with activation {gated!r} (known: {', '.join(ACTIVATIONS)})") from None
+
+
+def swiglu(gate_up, activation="silu"):
+    """``round(act(gate)) * up`` for ``gate_up = [gate | up]`` of shape ``[T, 2 * I]``."""
     _need(gate_up, "gate_up", None, 2)
     if gate_up.shape[1] % 2:
         raise KernelError(f"gate_up has an odd width {gate_up.shape[1]}")
     inner = gate_up.shape[1] // 2
     out = torch.empty((gate_up.shape[0], inner), dtype=gate_up.dtype, device=gate_up.device)
     rc = _lib("elementwise").sb_swiglu(
-        _code(gate_up.dtype), _ptr(gate_up), _ptr(out), gate_up.shape[0], inner, _stream())
+        _code(gate_up.dtype), _ptr(gate_up), _ptr(out), gate_up.shape[0], inner, gate_code(activation),
+        _stream())
     _check(rc, "swiglu")
     return out
 
@@ -200,8 +219,9 @@ def linear(x, weight, out_float=False, gated=False, status=None, add_to=None):
     ``round(add_to + round(product))`` in place and ``ADDED`` is returned; otherwise ``add_to`` is
     left alone and the product is returned as usual.
 
-    ``gated``: ``weight`` is ``[gate; up]`` stacked (``[2 * I, K]``) and the result is
-    ``round(silu(x @ gate.T)) * (x @ up.T)`` of shape ``[T, I]``.  ``out_float``
+    ``gated`` (True, or an activation of ``ACTIVATIONS`` by name; True means silu): ``weight`` is
+    ``[gate; up]`` stacked (``[2 * I, K]``) and the result is
+    ``round(act(x @ gate.T)) * (x @ up.T)`` of shape ``[T, I]``.  ``out_float``
     returns float32 whatever the working type (used for logits).  ``status`` (int32 ``[1]``) is the
     device word in which the tensor-core kernel reports a wait that ran out.
     """
@@ -211,6 +231,7 @@ def linear(x, weight, out_float=False, gated=False, status=None, add_to=None):
     if weight.shape[1] != k_dim:
         raise KernelError(f"weight {tuple(weight.shape)} does not take inputs of width {k_dim}")
     n_total = weight.shape[0]
+    gated = gate_code(gated)
     if gated and n_total % 2:
         raise KernelError(f"a gated weight needs an even number of rows, got {n_total}")
     n_out = n_total // 2 if gated else n_total
@@ -242,7 +263,7 @@ def linear(x, weight, out_float=False, gated=False, status=None, add_to=None):
         return linear_prompt(x, weight, gated=gated, status=status)
     else:
         y = torch.mm(x, weight.t())
-    return swiglu(y) if gated else y
+    return swiglu(y, gated) if gated else y
 
 
 def tensor_core_ok(x, weight, gated, n_out) -> bool:
@@ -322,6 +343,7 @@ def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=
     returns, bit 4 of ``status`` is set and the result is undefined."""
     _need(x, "x", torch.bfloat16, 2)
     _need(weight, "weight", torch.bfloat16, 2)
+    gated = gate_code(gated)
     rows, k_dim = x.shape
     n_total = weight.shape[0]
     n_out = n_total // 2 if gated else n_total
@@ -362,6 +384,7 @@ def linear_prompt(x, weight, gated=False, bn=0, pairs=0, status=None, withhold=N
     ``residual`` itself, which is returned."""
     _need(x, "x", torch.bfloat16, 2)
     _need(weight, "weight", torch.bfloat16, 2)
+    gated = gate_code(gated)
     rows, k_dim = x.shape
     n_total = weight.shape[0]
     n_out = n_total // 2 if gated else n_total
@@ -718,6 +741,220 @@ def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, hea
             _ptr(status), _stream())
     _check(rc, "attention_decode", 2 if n_splits > 1 and not in_cluster else 1)
     return out
+
+
+# ---------------------------------------------------------------------------------------- several streams
+
+def _f32(t, name, shape=None):
+    _need(t, name, torch.float32)
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
+def max_streams() -> int:
+    return _lib("streams").sb_max_streams()
+
+
+def embedding_streams(tokens, table, streams: int, status=None, fence=False):
+    """``out[t, s] = float(table[tokens[t]])`` for every stream ``s``: float32 ``[T, streams, H]``, the
+    residual streams of a model with hyper-connections at their start.  ``fence`` as in ``embedding``."""
+    _need(tokens, "tokens", torch.int32, 1)
+    _need(table, "table", None, 2)
+    out = torch.empty((tokens.shape[0], streams, table.shape[1]), dtype=torch.float32, device=table.device)
+    rc = _lib("streams").sb_embed_streams(
+        _code(table.dtype), _ptr(tokens), _ptr(table), _ptr(out), tokens.shape[0], table.shape[1],
+        table.shape[0], int(streams), _ptr(status), int(fence), _stream())
+    _check(rc, "embedding_streams")
+    return out
+
+
+def hyper_step(streams, dtype, pending=None, read=None, norm=None, rows=None):
+    """One kernel around a sublayer of a model with several residual streams (float32 ``[T, S, H]``).
+
+    ``pending = (y, mix, out, bias)``: the output ``y`` ``[T, H]`` of the sublayer before (``bias``
+    float32 ``[H]`` or None is added to it), which updates the streams, all at once from the old
+    ones, to ``x_t = sum_s mix[s, t] * x_s + out[t] * y``.  ``read``: float32 ``[S]``, the weights of
+    the sum ``u = sum_s read[s] * x_s`` that is returned (None: the plain sum of the streams).
+    ``norm = (alpha, weight, bias)`` makes it ``tanh(alpha * u) * weight + bias`` (Dynamic Tanh); None
+    returns ``u``.  The result is ``[T, H]`` in ``dtype``.  With ``rows`` (int32 ``[R]``) only those rows
+    are computed, the result is ``[R, H]`` and the streams are left as they were; without, the update
+    is written into ``streams``."""
+    _need(streams, "streams", torch.float32, 3)
+    n_tokens, n_streams, hidden = streams.shape
+    y = mix = out = bias = None
+    if pending is not None:
+        y, mix, out, bias = pending
+        _need(y, "y", dtype, 2)
+        if tuple(y.shape) != (n_tokens, hidden):
+            raise KernelError(f"y {tuple(y.shape)} does not match streams {tuple(streams.shape)}")
+        _f32(mix, "mix", (n_streams, n_streams))
+        _f32(out, "out", (n_streams,))
+        if bias is not None:
+            _f32(bias, "bias", (hidden,))
+    if read is not None:
+        _f32(read, "read", (n_streams,))
+    alpha = weight = shift = None
+    if norm is not None:
+        alpha, weight, shift = norm
+        _f32(alpha, "alpha")
+        _f32(weight, "norm weight", (hidden,))
+        _f32(shift, "norm bias", (hidden,))
+    n_rows = n_tokens
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n_rows = rows.shape[0]
+    normed = torch.empty((n_rows, hidden), dtype=dtype, device=streams.device)
+    rc = _lib("streams").sb_hyper_step(
+        _code(dtype), n_streams, _ptr(streams), _ptr(y), _ptr(bias), _ptr(mix), _ptr(out), _ptr(read),
+        int(norm is not None), _ptr(alpha), _ptr(weight), _ptr(shift), _ptr(normed), _ptr(rows), n_rows,
+        hidden, _stream())
+    if rc == -2:
+        raise KernelError(f"the stream kernels take 1 to {max_streams()} streams, not {n_streams}")
+    _check(rc, "hyper_step")
+    return normed
+
+
+def dynamic_tanh(x, alpha, weight, bias, delta=None, rows=None):
+    """``tanh(alpha * x) * weight + bias`` on the rows of ``x`` ``[T, H]``; ``delta`` and ``rows`` as in
+    ``rmsnorm`` (the residual sum in front of the norm, the norm of selected rows)."""
+    _need(x, "x", None, 2)
+    hidden = x.shape[1]
+    _f32(alpha, "alpha")
+    _f32(weight, "weight", (hidden,))
+    _f32(bias, "bias", (hidden,))
+    if delta is not None:
+        _need(delta, "delta", x.dtype, 2)
+        if delta.shape != x.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match x {tuple(x.shape)}")
+    n_rows = x.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n_rows = rows.shape[0]
+    out = torch.empty((n_rows, hidden), dtype=x.dtype, device=x.device)
+    rc = _lib("streams").sb_dyt(_code(x.dtype), _ptr(x), _ptr(delta), _ptr(alpha), _ptr(weight), _ptr(bias),
+                                _ptr(out), _ptr(rows), n_rows, hidden, _stream())
+    _check(rc, "dynamic_tanh")
+    return out
+
+
+# ---------------------------------------------------------------------------------------- differential attention
+
+DIFF_MAX_ROW = 256
+#: from this many tokens of one sequence in a step the tensor-core kernel is used
+DIFF_PREFILL_MIN_Q = 16
+
+
+def diff_prefill_takes(dtype, dim: int, v_dim: int) -> bool:
+    """Whether the tensor-core prompt kernel takes these sizes."""
+    return False
+
+
+def diff_prepare(proj, bias, heads, kv_heads, dim, v_dim, gate_width, temperature, tok_pos, tok_slot,
+                 block_table, k_store, v_store, write_cache=True):
+    """Finish the projections of a differential attention and file the new keys and values.
+
+    ``proj`` ``[T, heads * 2 * dim + gate_width (+ kv_heads * 2 * dim + kv_heads * v_dim)]`` is the
+    stacked product ``[q | gate | k | v]`` (the last two only with ``write_cache``); ``bias`` float32
+    of the same width or None.  Returns the queries ``[T, heads * 2 * dim]`` with their bias added and
+    scaled by ``1 + coef * ln(floor((p + 1) / every) + 1)`` at position ``p`` (``temperature = (coef,
+    every)`` or None).  Keys go to ``k_store`` ``[pages, kv_heads, 64, 2 * dim]``, values to ``v_store``
+    ``[pages, kv_heads, 64, v_dim]``; the gate columns are left where they are."""
+    _need(proj, "proj", None, 2)
+    n_tokens = proj.shape[0]
+    q_w = heads * 2 * dim
+    width = q_w + gate_width + (kv_heads * (2 * dim + v_dim) if write_cache else 0)
+    if proj.shape[1] != width:
+        raise KernelError(f"the stacked projection has width {proj.shape[1]}, expected {width}")
+    if bias is not None:
+        _f32(bias, "bias", (width,))
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    _need(tok_slot, "tok_slot", torch.int32, 1)
+    _need(block_table, "block_table", torch.int32, 2)
+    if write_cache:
+        _need(k_store, "key pages", proj.dtype, 4)
+        _need(v_store, "value pages", proj.dtype, 4)
+        if tuple(k_store.shape[1:]) != (kv_heads, PAGE_TOKENS, 2 * dim) or \
+                tuple(v_store.shape[1:]) != (kv_heads, PAGE_TOKENS, v_dim):
+            raise KernelError(f"cache pages have shapes {tuple(k_store.shape)} and {tuple(v_store.shape)}, expected "
+                              f"[pages, {kv_heads}, {PAGE_TOKENS}, {2 * dim}] and [pages, {kv_heads}, {PAGE_TOKENS}, {v_dim}]")
+    coef, every = temperature if temperature is not None else (0.0, 0)
+    q_out = torch.empty((n_tokens, q_w), dtype=proj.dtype, device=proj.device)
+    rc = _lib("attention_diff").sb_diff_prepare(
+        _code(proj.dtype), _ptr(proj), proj.shape[1], _ptr(bias), _ptr(q_out), _ptr(tok_pos), _ptr(tok_slot),
+        _ptr(block_table), block_table.shape[1], _ptr(k_store if write_cache else None),
+        _ptr(v_store if write_cache else None), n_tokens, heads, kv_heads, dim, v_dim, gate_width,
+        ctypes.c_float(coef), int(every), int(write_cache), _stream())
+    _check(rc, "diff_prepare")
+    return q_out
+
+
+def _diff_check(q, gate, k_store, v_store, heads, kv_heads, dim, v_dim):
+    _need(q, "q", None, 2)
+    if q.shape[1] != heads * 2 * dim:
+        raise KernelError(f"q has width {q.shape[1]}, expected {heads * 2 * dim}")
+    if 2 * dim > DIFF_MAX_ROW or v_dim > DIFF_MAX_ROW:
+        raise KernelError(f"differential attention takes 2 * dim and v_dim up to {DIFF_MAX_ROW}, got {2 * dim} and {v_dim}")
+    if heads % kv_heads:
+        raise KernelError(f"{heads} query heads cannot share {kv_heads} key/value heads")
+    _need(k_store, "key pages", q.dtype, 4)
+    _need(v_store, "value pages", q.dtype, 4)
+    if tuple(k_store.shape[1:]) != (kv_heads, PAGE_TOKENS, 2 * dim) or \
+            tuple(v_store.shape[1:]) != (kv_heads, PAGE_TOKENS, v_dim):
+        raise KernelError(f"cache pages have shapes {tuple(k_store.shape)} and {tuple(v_store.shape)}")
+    gate_stride = 0
+    if gate is not None:
+        if gate.dtype != q.dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[1] != heads * v_dim \
+                or gate.shape[0] != q.shape[0]:
+            raise KernelError(f"the gate must be [T, {heads * v_dim}] of {q.dtype} with unit column stride")
+        gate_stride = gate.stride(0)
+    return gate_stride
+
+
+def diff_attention(q, gate, k_store, v_store, block_table, tok_slot, tok_pos, heads, kv_heads, dim, v_dim,
+                   scale, lam, out_scale, eps, window=None, warps=None, kv_hint=0):
+    """Differential attention of each query row over its sequence's cached keys (csrc/attention_diff.cu):
+    per head ``o = a1 - lam * a2`` from two softmax maps over the same values, divided by its root mean
+    square over ``v_dim`` (``eps`` inside the root), times ``out_scale``, times ``sigmoid(gate)`` where
+    ``gate`` ``[T, heads * v_dim]`` (a view with a row stride is fine) is given.  One block per (row,
+    head); ``warps`` of it share the keys (chosen from ``kv_hint``, the longest sequence, when None)."""
+    gate_stride = _diff_check(q, gate, k_store, v_store, heads, kv_heads, dim, v_dim)
+    _need(block_table, "block_table", torch.int32, 2)
+    _need(tok_slot, "tok_slot", torch.int32, 1)
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    if warps is None:
+        warps = 1 if kv_hint <= 32 else 2 if kv_hint <= 128 else 4 if kv_hint <= 512 else 8
+    out = torch.empty((q.shape[0], heads * v_dim), dtype=q.dtype, device=q.device)
+    rc = _lib("attention_diff").sb_diff_attention(
+        _code(q.dtype), _ptr(q), _ptr(gate), int(gate_stride), _ptr(out), _ptr(k_store), _ptr(v_store),
+        _ptr(block_table), block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), q.shape[0], heads, kv_heads,
+        dim, v_dim, ctypes.c_float(scale), int(window or 0), ctypes.c_float(lam), ctypes.c_float(out_scale),
+        ctypes.c_float(eps), int(warps), _stream())
+    _check(rc, "diff_attention")
+    return out
+
+
+def diff_attention_step(q, gate, k_store, v_store, block_table, ctx, heads, kv_heads, dim, v_dim, scale, lam,
+                        out_scale, eps, window=None):
+    """The differential attention of one step, by the kernel that suits it: steps in which a sequence
+    brings many tokens run the bfloat16 tensor-core kernel (64 queries of a head a block); single
+    tokens, short chunks, the 32-bit path and sizes that kernel refuses run one block per (row, head)
+    whose warps share the keys."""
+    if (ctx.max_q_len >= DIFF_PREFILL_MIN_Q and ctx.host is not None
+            and diff_prefill_takes(q.dtype, dim, v_dim)):
+        return diff_attention_prefill(q, gate, k_store, v_store, block_table, ctx.seq_slot, ctx.seq_q_start,
+                                      ctx.seq_q_len, ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first, heads,
+                                      kv_heads, dim, v_dim, scale, lam, out_scale, eps, window)
+    return diff_attention(q, gate, k_store, v_store, block_table, ctx.tok_slot, ctx.tok_pos, heads, kv_heads,
+                          dim, v_dim, scale, lam, out_scale, eps, window, kv_hint=ctx.max_kv_len)
+
+
+def add_bias(y, bias):
+    """``y += bias`` in place (``bias`` float32 ``[N]``, the sum rounded once to ``y``'s type)."""
+    _need(y, "y", None, 2)
+    _f32(bias, "bias", (y.shape[1],))
+    rc = _lib("streams").sb_add_bias(_code(y.dtype), _ptr(y), _ptr(bias), y.shape[0], y.shape[1], _stream())
+    _check(rc, "add_bias")
+    return y
 
 
 # ---------------------------------------------------------------------------------------- sampling

@@ -1,10 +1,14 @@
 from .attention import GroupedQueryAttention
+from .attention_diff import DifferentialAttention
 from .base import ROLES, ParamSpec, Part, Role, register_role, role_of
 from .block import PreNormBlock
 from .feedforward import GatedFeedForward
+from .hyper import HyperConnection, HyperMixerOnlyBlock, HyperPreNormBlock, Pending
 from .norm import RMSNorm
+from .norm_dyt import DynamicTanh
 from .registry import FAMILIES, lookup, register
 from .rotary import Rotation, RotaryTable
 
-__all__ = ["FAMILIES", "ROLES", "Role", "register_role", "role_of", "GatedFeedForward", "GroupedQueryAttention", "ParamSpec", "Part",
+__all__ = ["FAMILIES", "ROLES", "Role", "register_role", "role_of", "GatedFeedForward", "GroupedQueryAttention", "DifferentialAttention", "DynamicTanh", "HyperConnection",
+           "HyperMixerOnlyBlock", "HyperPreNormBlock", "Pending", "ParamSpec", "Part",
            "PreNormBlock", "RMSNorm", "RotaryTable", "Rotation", "lookup", "register"]

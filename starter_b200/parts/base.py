@@ -17,11 +17,14 @@ import torch
 class Role:
     """What a kind of tensor is drawn from in the random-weights mode (``mean``, ``std``) and how it is
     placed on the device: ``keep_32bit`` tensors that the checkpoint stores in 32-bit stay so (the
-    others are cast to the working type)."""
+    others are cast to the working type); ``always_32bit`` tensors are float32 on the device however
+    they are stored (what enters a 32-bit computation: norm parameters, stream weights, biases that a
+    kernel adds in float)."""
 
     mean: float
     std: float
     keep_32bit: bool = False
+    always_32bit: bool = False
 
 
 #: the roles a parameter can have.  ``matrix``: a projection, N(0, 0.02), working type.  ``gain``: a
@@ -34,6 +37,12 @@ ROLES = {
     "gain": Role(1.0, 0.1, keep_32bit=True),
     "bias": Role(0.0, 0.02, keep_32bit=True),
     "state": Role(0.0, 0.1, keep_32bit=True),
+    # float32 on the device whatever the checkpoint stores
+    "gain32": Role(1.0, 0.1, always_32bit=True),
+    "bias32": Role(0.0, 0.02, always_32bit=True),
+    "slope": Role(0.5, 0.1, always_32bit=True),          # the scalar inside a Dynamic Tanh
+    "vector32": Role(0.0, 0.1, always_32bit=True),       # small learnt vectors (lambda's factors)
+    "stream_weight": Role(0.25, 0.2, always_32bit=True),  # how streams are read, written and mixed
 }
 
 

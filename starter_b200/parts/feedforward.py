@@ -1,4 +1,5 @@
-"""Dense gated feed-forward: ``down(round(silu(gate(x))) * up(x))``, no biases, no routing."""
+"""Dense gated feed-forward: ``down(round(act(gate(x))) * up(x))`` with silu or the tanh form of gelu,
+no biases, no routing."""
 
 from __future__ import annotations
 
@@ -14,8 +15,9 @@ class GatedFeedForward(Part):
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
-        if spec.activation != "silu":
-            raise ValueError(f"the gated feed-forward kernel implements silu, not {spec.activation!r}")
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"the gated feed-forward kernels implement {', '.join(ops.ACTIVATIONS)}, "
+                             f"not {spec.activation!r}")
 
     def param_specs(self):
         h, i = self.spec.hidden_size, self.spec.intermediate_size
@@ -29,7 +31,7 @@ class GatedFeedForward(Part):
 
     def __call__(self, x, ctx=None, add_to=None):
         status = ctx.status if ctx is not None else None
-        act = ops.linear(x, self.gate_up, gated=True, status=status)
+        act = ops.linear(x, self.gate_up, gated=self.spec.activation, status=status)
         return ops.linear(act, self.down, status=status, add_to=add_to)
 
     def weight_bytes(self):

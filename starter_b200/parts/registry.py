@@ -14,6 +14,8 @@ Families and their interfaces
   position      ``__init__(spec, dtype, device)``; ``ensure(length)`` -> True if device tables moved;
                 ``rotation()`` -> ``Rotation`` (tables, how many dimensions of a head they turn and
                 in which layout) for mixers that rotate queries and keys
+  connection    ``__init__(spec, dtype)``; ``param_specs()``, ``set_params``; ``open(streams, pending, norm,
+                dtype)`` -> a sublayer's normed input (for arrangements over several residual streams)
   arrangement   class attribute ``FAMILIES`` (part name -> family); ``__init__(parts: dict)``;
                 ``parts()``; attribute ``mixer`` (the part that owns the layer's cache entry);
                 ``__call__(residual, pending, ctx, entry, writes_cache)`` -> ``(residual, pending)``
@@ -22,12 +24,15 @@ Families and their interfaces
 from __future__ import annotations
 
 from .attention import GroupedQueryAttention
+from .attention_diff import DifferentialAttention
 from .block import PreNormBlock
 from .feedforward import GatedFeedForward
+from .hyper import HyperConnection, HyperMixerOnlyBlock, HyperPreNormBlock
 from .norm import RMSNorm
+from .norm_dyt import DynamicTanh
 from .rotary import RotaryTable
 
-FAMILIES = ("mixer", "feed_forward", "norm", "position", "arrangement")
+FAMILIES = ("mixer", "feed_forward", "norm", "position", "connection", "arrangement")
 _REGISTRY = {family: {} for family in FAMILIES}
 
 
@@ -50,3 +55,8 @@ register("feed_forward", "gated_dense", GatedFeedForward)
 register("norm", "rmsnorm", RMSNorm)
 register("position", "rope", RotaryTable)
 register("arrangement", "prenorm", PreNormBlock)
+register("mixer", "differential_attention", DifferentialAttention)
+register("norm", "dynamic_tanh", DynamicTanh)
+register("connection", "hyper", HyperConnection)
+register("arrangement", "hyper_prenorm", HyperPreNormBlock)
+register("arrangement", "hyper_mixer_only", HyperMixerOnlyBlock)

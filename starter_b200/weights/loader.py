@@ -44,6 +44,8 @@ def place(tensor: torch.Tensor, role: str, dtype, device) -> torch.Tensor:
     """Move one stored tensor to the device in the dtype its role calls for."""
     if not tensor.dtype.is_floating_point:
         return tensor.to(device=device, dtype=torch.int32)
+    if role_of(role).always_32bit:
+        return tensor.to(device=device, dtype=torch.float32)
     if role_of(role).keep_32bit and tensor.dtype in (torch.float32, torch.float64):
         return tensor.to(device=device, dtype=torch.float32)
     return tensor.to(device=device, dtype=dtype)
@@ -84,16 +86,17 @@ class CheckpointTensors(Mapping):
         return default
 
 
-def load_checkpoint(model_dir: str, expected: dict, dtype, device, tied_alias=None):
+def load_checkpoint(model_dir: str, expected: dict, dtype, device, tied_alias=None, ignored=()):
     """Check the checkpoint against ``expected`` and return a mapping ``name -> device tensor`` that
     reads and places each tensor when it is indexed.
 
     ``tied_alias = (alias, target)``: ``alias`` is not expected; if the checkpoint
-    holds it anyway it must equal ``target`` exactly, else that is reported.
+    holds it anyway it must equal ``target`` exactly, else that is reported.  ``ignored``: names
+    that may be stored and are not read.
     """
     owners = open_model_files(model_dir)
     stored = {name: handle.entries[name] for name, handle in owners.items()}
-    optional = (tied_alias[0],) if tied_alias else ()
+    optional = ((tied_alias[0],) if tied_alias else ()) + tuple(ignored)
     missing, unexpected, wrong, other = check_names(expected, stored, optional)
     if tied_alias and tied_alias[0] in stored and tied_alias[1] in stored and not (missing or wrong):
         alias, target = tied_alias

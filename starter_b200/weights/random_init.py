@@ -50,7 +50,10 @@ class RandomTensors(Mapping):
         return len(self._expected)
 
     def __getitem__(self, name):
-        return random_tensor(self._seed, name, self._expected[name], self._dtype, self._device)
+        spec = self._expected[name]
+        # placed as the loader would place it: what always computes in 32-bit is float32
+        dtype = torch.float32 if role_of(spec.role).always_32bit else self._dtype
+        return random_tensor(self._seed, name, spec, dtype, self._device)
 
     def pop(self, name, default=None):
         return default
