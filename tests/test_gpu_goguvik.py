@@ -1,0 +1,410 @@
+"""Goguvik on the GPU against the plain statement: each mechanism alone, then the model through the
+step function, the cache and the generation loop, cut into steps and batches in every way."""
+
+import math
+
+import pytest
+import torch
+
+import plain_goguvik as plain
+from gpu_helpers import DTYPES, assert_close
+from tiny import random_prompt
+from tiny_goguvik import TINY_G, make_goguvik_folder
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = ["GA", "GB", "GC"]
+TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+_cases, _runners = {}, {}
+
+
+def case(tmp_path_factory, name, seed=1):
+    if (name, seed) not in _cases:
+        folder = make_goguvik_folder(tmp_path_factory.mktemp(f"g{name}{seed}"), name, seed=seed)
+        _cases[(name, seed)] = (folder,) + plain.read_model_folder(folder)
+    return _cases[(name, seed)]
+
+
+def runner_for(tmp_path_factory, name, dtype, max_tokens=64 * 40):
+    from starter_b200.engine import ModelRunner, load_model
+
+    if (name, dtype) not in _runners:
+        folder, _, _ = case(tmp_path_factory, name)
+        _runners[(name, dtype)] = ModelRunner(load_model(folder, dtype), max_tokens=max_tokens, max_sequences=12)
+    return _runners[(name, dtype)]
+
+
+def close(got, want, dtype, what, fp32=2e-5, bf16=2e-2):
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    tol = (fp32 if dtype in ("float32", torch.float32) else bf16) * float(want.abs().max())
+    err = (got - want).abs()
+    assert float(err.max()) <= tol, f"{what}: off by {float(err.max()):.3e} (allowed {tol:.3e}) at {tuple(int(i) for i in (err == err.max()).nonzero()[0])}"
+
+
+# ------------------------------------------------------------------------------ mechanisms alone
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_dynamic_tanh_alone(dtype):
+    from starter_b200 import ops
+
+    t = TORCH[dtype]
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(9, 72, generator=g, dtype=torch.float64) * 2
+    d = torch.randn(9, 72, generator=g, dtype=torch.float64)
+    alpha = torch.tensor(0.7, dtype=torch.float64)
+    w, b = torch.randn(72, generator=g, dtype=torch.float64), torch.randn(72, generator=g, dtype=torch.float64)
+    dev = lambda v, ty=torch.float32: v.to("cuda", ty).contiguous()  # noqa: E731
+    xd, dd = dev(x, t), dev(d, t)
+    args = (dev(alpha).reshape(1), dev(w), dev(b))
+    close(ops.dynamic_tanh(xd, *args), plain.plain_dynamic_tanh(xd.double().cpu(), alpha, w, b), dtype, "norm alone")
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device="cuda")
+    both = (xd.double().cpu() + dd.double().cpu()).to(t).double()
+    close(ops.dynamic_tanh(xd, *args, delta=dd, rows=rows), plain.plain_dynamic_tanh(both[[8, 0, 3]], alpha, w, b), dtype, "rows")
+    assert torch.equal(xd, dev(x, t)), "selected rows must leave the stream alone"
+    close(ops.dynamic_tanh(xd, *args, delta=dd), plain.plain_dynamic_tanh(both, alpha, w, b), dtype, "sum and norm")
+    close(xd, both, dtype, "the sum is written back", bf16=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("streams", [1, 2, 3, 4, 5, 8])
+def test_stream_step_alone(streams, dtype):
+    """The pending write, the next read and the norm in one kernel; the matrix is [from, to], every
+    stream is formed from the OLD ones, and selected rows leave the streams as they were."""
+    from starter_b200 import ops
+
+    t = TORCH[dtype]
+    g = torch.Generator().manual_seed(10 + streams)
+    rnd = lambda *shape: torch.randn(*shape, generator=g, dtype=torch.float64)  # noqa: E731
+    x, y = rnd(7, streams, 40), rnd(7, 40)
+    mix, out, read, bias = rnd(streams, streams), rnd(streams), rnd(streams), rnd(40)
+    alpha, w, b = torch.tensor(0.4, dtype=torch.float64), rnd(40), rnd(40)
+    dev = lambda v, ty=torch.float32: v.to("cuda", ty).contiguous()  # noqa: E731
+    xd, yd = dev(x), dev(y, t)
+    y_seen = yd.double().cpu()
+    x_seen = xd.double().cpu()
+    norm = (dev(alpha).reshape(1), dev(w), dev(b))
+    new = plain.plain_stream_write(x_seen, y_seen + bias, mix, out)
+    rows = torch.tensor([6, 2], dtype=torch.int32, device="cuda")
+    # the model's end on selected rows: write, plain sum, norm; nothing stored
+    got = ops.hyper_step(xd, t, (yd, dev(mix), dev(out), dev(bias)), None, norm, rows=rows)
+    close(got, plain.plain_dynamic_tanh(new[[6, 2]].sum(1), alpha, w, b), dtype, "closing rows")
+    assert torch.equal(xd, dev(x))
+    # write, read, norm
+    got = ops.hyper_step(xd, t, (yd, dev(mix), dev(out), dev(bias)), dev(read), norm)
+    close(got, plain.plain_dynamic_tanh(plain.plain_stream_read(new, read), alpha, w, b), dtype, "write, read, norm")
+    close(xd, new, "float32", "the streams after the write", fp32=1e-5)
+    # a read with nothing pending and no norm
+    got = ops.hyper_step(xd, t, None, dev(read), None)
+    close(got, plain.plain_stream_read(xd.double().cpu(), read), dtype, "read alone")
+
+
+def test_more_streams_than_the_kernel_takes_are_refused():
+    from starter_b200 import ops
+
+    x = torch.zeros(2, ops.max_streams() + 1, 8, device="cuda")
+    with pytest.raises(ops.KernelError, match="streams"):
+        ops.hyper_step(x, torch.float32, None, None, None)
+
+
+def test_embedding_into_streams():
+    from starter_b200 import ops
+
+    table = torch.randn(11, 24, device="cuda").to(torch.bfloat16)
+    tokens = torch.tensor([3, 10, 0], dtype=torch.int32, device="cuda")
+    got = ops.embedding_streams(tokens, table, 3)
+    assert got.dtype == torch.float32 and tuple(got.shape) == (3, 3, 24)
+    for s in range(3):
+        assert torch.equal(got[:, s], table[tokens.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows", [3, 40, 200, 600])
+def test_gated_product_with_tanh_gelu(rows, dtype):
+    """Every product kernel's gated epilogue knows the second activation (few rows, 128-row tiles, the
+    library product followed by the activation kernel, the prompt product)."""
+    from starter_b200 import ops
+
+    t = TORCH[dtype]
+    g = torch.Generator().manual_seed(rows)
+    x = (torch.randn(rows, 64, generator=g) * 1.5).to("cuda", t)
+    w = (torch.randn(2 * 128, 64, generator=g) * 0.3).to("cuda", t)
+    got = ops.linear(x, w, gated="gelu_tanh")
+    xs, ws = x.double().cpu(), w.double().cpu()
+    gate, up = xs @ ws[:128].T, xs @ ws[128:].T
+    if dtype == "bfloat16":
+        gate, up = gate.to(t).double(), up.to(t).double()
+    close(got, plain.plain_gelu_tanh(gate) * up, dtype, f"{rows} rows", bf16=1.2e-2)
+    silu = ops.linear(x, w, gated=True)
+    close(silu, torch.nn.functional.silu(gate) * up, dtype, f"{rows} rows, silu as before", bf16=1.2e-2)
+
+
+class Pages:
+    """A cache by hand: one sequence whose pages are scattered, keys of both maps in one row."""
+
+    def __init__(self, length, groups, dim, vdim, dtype, seed):
+        g = torch.Generator().manual_seed(seed)
+        self.k = torch.randn(length, groups, 2, dim, generator=g, dtype=torch.float64)
+        self.v = torch.randn(length, groups, vdim, generator=g, dtype=torch.float64)
+        self.length, self.groups, self.dim, self.vdim, self.t = length, groups, dim, vdim, TORCH[dtype]
+
+    def store(self):
+        n_pages = -(-self.length // 64)
+        order = torch.randperm(n_pages + 3, generator=torch.Generator().manual_seed(5))[:n_pages]
+        ks = torch.full((n_pages + 3, self.groups, 64, 2 * self.dim), 7.0, dtype=self.t, device="cuda")
+        vs = torch.full((n_pages + 3, self.groups, 64, self.vdim), -9.0, dtype=self.t, device="cuda")
+        for j in range(self.length):
+            ks[order[j // 64], :, j % 64] = self.k[j].reshape(self.groups, -1).to("cuda", self.t)
+            vs[order[j // 64], :, j % 64] = self.v[j].to("cuda", self.t)
+        table = torch.zeros(2, n_pages, dtype=torch.int32, device="cuda")
+        table[1] = order.to(torch.int32)
+        self.k = torch.stack([ks[order[j // 64], :, j % 64].double().cpu().view(self.groups, 2, self.dim) for j in range(self.length)])
+        self.v = torch.stack([vs[order[j // 64], :, j % 64].double().cpu() for j in range(self.length)])
+        return ks, vs, table
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, groups, dim, vdim", [(4, 2, 16, 24), (3, 3, 8, 40), (6, 1, 24, 16), (2, 1, 64, 128)])
+def test_attention_alone_with_one_key_that_stands_out(heads, groups, dim, vdim, dtype):
+    """Among 700 keys one is made to dominate map 1 and another map 2 (its query direction scaled up):
+    far back, on either side of a page border, the newest.  A key that a kernel skips or reads from
+    the wrong page changes the answer by the whole value."""
+    from starter_b200 import ops
+
+    t = TORCH[dtype]
+    pages = Pages(700, groups, dim, vdim, dtype, seed=dim)
+    ks, vs, table = pages.store()
+    lam, lam0, eps, scale = 0.55, 0.3, 1e-5, 0.3
+    for star1, star2 in ((2, 690), (63, 64), (64, 63), (699, 0), (127, 128), (640, 639)):
+        for positions in ([699], [690, 691, 692, 693, 694, 695, 696, 697, 698, 699], [64, 63, 699, 128]):
+            g = torch.Generator().manual_seed(star1)
+            q = torch.randn(len(positions), heads, 2, dim, generator=g, dtype=torch.float64) * 0.3
+            for h in range(heads):
+                grp = h // (heads // groups)
+                q[:, h, 0] += 6.0 * pages.k[star1, grp, 0] / scale / dim
+                q[:, h, 1] += 6.0 * pages.k[star2, grp, 1] / scale / dim
+            gate = torch.randn(len(positions), heads * vdim, generator=g, dtype=torch.float64)
+            qd = q.reshape(len(positions), -1).to("cuda", t).contiguous()
+            wide = torch.zeros(len(positions), heads * vdim + 5, dtype=t, device="cuda")   # a gate with a row stride
+            wide[:, :heads * vdim] = gate.to("cuda", t)
+            pos = torch.tensor(positions, dtype=torch.int32, device="cuda")
+            slot = torch.ones(len(positions), dtype=torch.int32, device="cuda")
+            qs = qd.double().cpu().view(len(positions), heads, 2, dim)
+            gs = wide[:, :heads * vdim].double().cpu()
+            for warps in (1, 3, 8):
+                got = ops.diff_attention(qd, wide[:, :heads * vdim], ks, vs, table, slot, pos, heads, groups, dim, vdim,
+                                         scale, lam, 1 - lam0, eps, warps=warps)
+                want = torch.cat([plain.plain_differential_head(
+                    qs[:, h, 0], qs[:, h, 1], pages.k[:, h // (heads // groups), 0], pages.k[:, h // (heads // groups), 1],
+                    pages.v[:, h // (heads // groups)], scale, lam, lam0, eps, torch.tensor(positions)) for h in range(heads)], -1)
+                # a1 - lam * a2 cancels in part and the unit norm divides by what is left: float32 sums of
+                # 64 products in the scores show up a few times larger than in the other tests
+                close(got, want * torch.sigmoid(gs), dtype, f"keys {star1}/{star2}, queries at {positions}, {warps} warps",
+                      fp32=1e-4)
+    # a window: the key just inside is seen, the key just outside is not
+    qd = torch.zeros(1, heads * 2 * dim, dtype=t, device="cuda")
+    pos = torch.tensor([500], dtype=torch.int32, device="cuda")
+    slot = torch.ones(1, dtype=torch.int32, device="cuda")
+    got = ops.diff_attention(qd, None, ks, vs, table, slot, pos, heads, groups, dim, vdim, scale, 0.0, 1.0, 0.0, window=3)
+    mean = pages.v[498:501].mean(0)
+    want = torch.cat([mean[h // (heads // groups)] for h in range(heads)])
+    want = (want.view(heads, vdim) / want.view(heads, vdim).pow(2).mean(-1, keepdim=True).sqrt()).reshape(1, -1)
+    close(got, want, dtype, "a window of three keys")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prepare_alone(dtype):
+    """Biases, the temperature on both sides of every step of its quotient, and keys and values filed
+    at their own places across a page border."""
+    from starter_b200 import ops
+
+    t = TORCH[dtype]
+    heads, groups, dim, vdim, every, coef = 3, 1, 8, 12, 8, 0.75
+    gate_w = heads * vdim
+    width = heads * 2 * dim + gate_w + groups * (2 * dim + vdim)
+    positions = [0, 6, 7, 8, 14, 15, 16, 62, 63, 64, 65, 127, 128]
+    g = torch.Generator().manual_seed(1)
+    proj = torch.randn(len(positions), width, generator=g).to("cuda", t)
+    bias = torch.randn(width, generator=g).to("cuda")
+    bias[heads * 2 * dim: heads * 2 * dim + gate_w] = 0
+    ks = torch.zeros(5, groups, 64, 2 * dim, dtype=t, device="cuda")
+    vs = torch.zeros(5, groups, 64, vdim, dtype=t, device="cuda")
+    table = torch.tensor([[0, 0, 0], [4, 1, 3]], dtype=torch.int32, device="cuda")
+    pos = torch.tensor(positions, dtype=torch.int32, device="cuda")
+    slot = torch.ones(len(positions), dtype=torch.int32, device="cuda")
+    q = ops.diff_prepare(proj, bias, heads, groups, dim, vdim, gate_w, (coef, every), pos, slot, table, ks, vs)
+    full = proj.double().cpu() + bias.double().cpu()
+    temp = plain.plain_query_temperature(torch.tensor(positions, dtype=torch.float64), coef, every)
+    close(q, full[:, :heads * 2 * dim] * temp[:, None], dtype, "queries")
+    k0 = heads * 2 * dim + gate_w
+    for i, p in enumerate(positions):
+        page = [4, 1, 3][p // 64]
+        close(ks[page, :, p % 64].reshape(-1), full[i, k0:k0 + groups * 2 * dim], dtype, f"key at {p}")
+        close(vs[page, :, p % 64].reshape(-1), full[i, k0 + groups * 2 * dim:], dtype, f"value at {p}")
+    assert float(ks[0].abs().max()) == 0.0 and float(ks[2].abs().max()) == 0.0
+    # a layer that only reads: queries (and gate) alone, nothing filed
+    before = ks.clone()
+    q2 = ops.diff_prepare(proj[:, :k0].contiguous(), bias[:k0].contiguous(), heads, groups, dim, vdim, gate_w, None,
+                          pos, slot, table, None, None, write_cache=False)
+    close(q2, full[:, :heads * 2 * dim], dtype, "queries without temperature")
+    assert torch.equal(ks, before)
+
+
+# ------------------------------------------------------------------------------ the model
+
+def all_places(n):
+    return list(range(n))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_each_request_alone_and_whole(tmp_path_factory, name, dtype):
+    from starter_b200.engine import StepEntry
+
+    _, cfg, w = case(tmp_path_factory, name)
+    runner = runner_for(tmp_path_factory, name, dtype)
+    for length, seed in ((1, 1), (2, 2), (9, 3), (64, 4), (65, 5), (200, 6)):
+        prompt = random_prompt(length, cfg["vocab"], seed)
+        slot = runner.open_sequence()
+        got = runner.step([StepEntry(slot, prompt, all_places(length))])
+        runner.close_sequence(slot)
+        want = plain.plain_forward(cfg, w, prompt)
+        assert_close(got, want, dtype, f"{name} whole, length {length}")
+        assert_close(got[:3], want[:3], dtype, f"{name}: the first tokens of a sequence")
+    runner.check_status()
+    runner.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_every_layer_against_the_plain_layers(tmp_path_factory, dtype):
+    """The sum of the streams after each layer, which names the first layer that differs."""
+    from starter_b200 import ops
+    from starter_b200.engine import StepEntry
+
+    _, cfg, w = case(tmp_path_factory, "GA")
+    runner = runner_for(tmp_path_factory, "GA", dtype)
+    model = runner.model
+    prompt = random_prompt(37, cfg["vocab"], 8)
+    _, want = plain.plain_forward(cfg, w, prompt, return_layers=True)
+    slot = runner.open_sequence()
+    ctx = runner.make_context([StepEntry(slot, prompt, [])])
+    streams = ops.embedding_streams(ctx.tokens, model.embed, model.spec.streams, ctx.status)
+    pending = None
+    rows = torch.arange(len(prompt), dtype=torch.int32, device="cuda")
+    for i, entry in enumerate(model.spec.schedule):
+        streams, pending = model.blocks[entry.layer](streams, pending, ctx, entry.cache, entry.writes_cache)
+        total = ops.hyper_step(streams, torch.float32, (pending.value.float(),) + pending.for_kernel()[1:], None, None, rows=rows)
+        close(total, want[i], dtype, f"after layer {i}", fp32=2e-5, bf16=2.5e-2)
+    runner.close_sequence(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_prompt_then_tokens_one_by_one(tmp_path_factory, name, dtype):
+    """The temperature's steps (every 8, 5 or 64 positions) and a page border are crossed while decoding."""
+    from starter_b200.engine import StepEntry
+
+    _, cfg, w = case(tmp_path_factory, name)
+    runner = runner_for(tmp_path_factory, name, dtype)
+    for length, tail in ((40, 39), (100, 45), (150, 24)):
+        prompt = random_prompt(length, cfg["vocab"], 10 + length)
+        want = plain.plain_forward(cfg, w, prompt)
+        slot = runner.open_sequence()
+        head = length - tail
+        rows = [runner.step([StepEntry(slot, prompt[:head], all_places(head))])]
+        for tok in prompt[head:]:
+            rows.append(runner.step([StepEntry(slot, [tok], [0])]))
+        runner.close_sequence(slot)
+        got = torch.cat(rows)
+        assert_close(got, want, dtype, f"{name} last {tail} one by one, length {length}")
+        assert_close(got[head:head + 1], want[head:head + 1], dtype, "the first single-token step")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_portions_of_several_sizes(tmp_path_factory, name, dtype):
+    from starter_b200.engine import StepEntry
+
+    _, cfg, w = case(tmp_path_factory, name)
+    runner = runner_for(tmp_path_factory, name, dtype)
+    prompt = random_prompt(171, cfg["vocab"], 77)
+    want = plain.plain_forward(cfg, w, prompt)
+    for sizes in ((2, 2, 3, 57, 64, 1, 40, 2), (63, 2, 63, 43), (5, 128, 38)):
+        slot = runner.open_sequence()
+        rows, at = [], 0
+        for n in sizes:
+            rows.append(runner.step([StepEntry(slot, prompt[at:at + n], all_places(n))]))
+            at += n
+        assert at == len(prompt)
+        runner.close_sequence(slot)
+        assert_close(torch.cat(rows), want, dtype, f"{name} portions {sizes}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_unequal_batches_with_slots_and_pages_used_again(tmp_path_factory, name, dtype):
+    from starter_b200.engine import StepEntry
+
+    _, cfg, w = case(tmp_path_factory, name)
+    runner = runner_for(tmp_path_factory, name, dtype)
+    vocab = cfg["vocab"]
+    batches = [[(70, 9), (5, 3), (33, 12), (1, 6)], [(2, 40), (129, 2), (64, 5)], [(17, 0), (63, 3)]]
+    seed = 300
+    for batch in batches:
+        seqs, slots, got = [], [], []
+        for plen, extra in batch:
+            seed += 1
+            seqs.append(random_prompt(plen + extra, vocab, seed))
+            slots.append(runner.open_sequence())
+            got.append([])
+        first = runner.step([StepEntry(slots[i], seqs[i][:plen], all_places(plen)) for i, (plen, _) in enumerate(batch)])
+        offset = 0
+        for i, (plen, _) in enumerate(batch):
+            got[i].append(first[offset:offset + plen])
+            offset += plen
+        live = [i for i, (_, extra) in enumerate(batch) if extra > 0]
+        for i, (_, extra) in enumerate(batch):
+            if extra == 0:
+                runner.close_sequence(slots[i])
+        step = 0
+        while live:
+            out = runner.step([StepEntry(slots[i], [seqs[i][batch[i][0] + step]], [0]) for i in live])
+            for row, i in enumerate(live):
+                got[i].append(out[row:row + 1])
+            step += 1
+            for i in [i for i in live if batch[i][1] == step]:
+                runner.close_sequence(slots[i])
+            live = [i for i in live if batch[i][1] > step]
+        for i, seq in enumerate(seqs):
+            assert_close(torch.cat(got[i]), plain.plain_forward(cfg, w, seq), dtype, f"{name} batch {batch}, request {i}")
+        runner.cache.check()
+    assert runner.cache.slots.held_count == 0 and runner.cache.pages.held_count == 0
+
+
+@pytest.mark.parametrize("name", ["GA", "GC"])
+def test_greedy_generation_through_the_entry_point(tmp_path_factory, name):
+    """Unequal prompts through ``Engine.generate`` (the scheduler, the captured single-token step, the
+    sampler): 70 tokens each, past a page border and several temperature steps, equal to the plain
+    statement's greedy continuation."""
+    from starter_b200 import Engine
+
+    folder, cfg, w = case(tmp_path_factory, name)
+    engine = Engine(folder, dtype="float32", max_batch=4)
+    prompts = [random_prompt(n, cfg["vocab"], 900 + n) for n in (50, 3, 21)]
+    steps = list(engine.generate(prompts, 70))
+    assert len(steps) == 70
+    for i, prompt in enumerate(prompts):
+        assert [s[i] for s in steps] == plain.plain_generate(cfg, w, prompt, 70), f"request {i}"
+
+
+def test_random_weights_from_the_library_run_in_bfloat16(tmp_path_factory):
+    """``random_model`` places every tensor as the loader would, and sampling with temperature runs."""
+    from starter_b200 import Engine
+    from starter_b200.config import config_from_dict
+    from starter_b200.engine.runner import random_model
+
+    model = random_model(config_from_dict(TINY_G["GA"]), seed=5, dtype="bfloat16")
+    engine = Engine.from_model(model, max_batch=2)
+    out = engine.complete([[1, 2, 3], [4]], 12, temperature=0.8, seed=3)
+    assert [len(c.tokens) for c in out] == [12, 12]
+    assert all(0 <= t < 200 for c in out for t in c.tokens)
