@@ -1,0 +1,336 @@
+// Differential attention for steps in which a sequence brings many tokens: bfloat16, tensor cores.
+//
+// A block takes 64 queries of one query head (four warps of 16 rows) and walks the sequence's cache
+// pages once.  A page's key rows hold both maps, [k1 | k2] of `dim` each, so the two score tiles
+// S1 = Q1 K1^T and S2 = Q2 K2^T come from the same shared-memory tile (different 16-column steps of
+// it); each map has its own running maximum, sum and accumulator, and a page's values are read from
+// shared memory once for both maps' P V products.  At the end the block forms
+//     o = O1 / l1 - lambda * O2 / l2,   o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate)
+// per row (a row's columns lie in the four lanes of a quad) and writes bfloat16.
+// Scores, weights, sums and both accumulators are float; products use mma.sync.m16n8k16 (bf16 in,
+// float accumulate); tiles are staged with cp.async, two pages in flight, in the swizzled layout of the
+// single-map prompt kernel.  Sizes: dim a multiple of 16 up to 128, v_dim a multiple of 16 up to 128.
+#include "common.cuh"
+
+#define DP_BQ 64
+#define DP_THREADS 128
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte column `chunk` of `row` in a [rows][D] bfloat16 tile with swizzled columns.
+template <int D> __device__ __forceinline__ int tile_offset(int row, int chunk) {
+  constexpr int C = D / 8;
+  const int sw = C >= 8 ? (row & 7) : ((row / (8 / C)) % C);
+  return row * D * 2 + ((chunk ^ sw) << 4);
+}
+
+struct DiffPrefillTail {
+  float lambda, out_scale, eps;
+};
+
+template <int QK, int VD>
+__global__ void __launch_bounds__(DP_THREADS)
+diff_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate, int gate_stride,
+                    bf16* __restrict__ out, const bf16* __restrict__ k_store, const bf16* __restrict__ v_store,
+                    const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slot,
+                    const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                    const int* __restrict__ seq_kv_len, const int* __restrict__ tile_seq,
+                    const int* __restrict__ tile_first, int heads, int kv_heads, float scale_log2, int window,
+                    DiffPrefillTail tail) {
+  constexpr int CQ = QK / 8, CV = VD / 8;
+  constexpr int K_BYTES = SB_PAGE_TOKENS * QK * 2, V_BYTES = SB_PAGE_TOKENS * VD * 2;
+  constexpr int KSTEPS = QK / 32;  // 16-column steps of one map's Q.K^T (dim / 16)
+  constexpr int NBLK = VD / 8;     // 8-wide column blocks of the output
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* q_tile = smem;                       // [64][QK]
+  uint8_t* k_tiles = smem + DP_BQ * QK * 2;     // 2 x [64][QK]
+  uint8_t* v_tiles = k_tiles + 2 * K_BYTES;     // 2 x [64][VD]
+
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(q);
+  SB_BEHIND_WAIT(gate);
+  SB_BEHIND_WAIT(k_store);
+  SB_BEHIND_WAIT(v_store);
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int seq = tile_seq[tile];
+  const int q_first = tile_first[tile];
+  const int q_len = seq_q_len[seq], kv_len = seq_kv_len[seq];
+  const int rows_valid = min(DP_BQ, q_len - q_first);
+  const int pos0 = kv_len - q_len + q_first;    // absolute position of the tile's first query
+  const int kvh = head / (heads / kv_heads);
+  const int* pages = block_table + (size_t)seq_slot[seq] * table_stride;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  const int hi = pos0 + rows_valid - 1;                                   // last key any row sees
+  int lo = 0;
+  if (window > 0 && pos0 - window + 1 > 0) lo = pos0 - window + 1;        // first key any row sees
+  const int page_lo = lo / SB_PAGE_TOKENS, page_hi = hi / SB_PAGE_TOKENS;
+  const int n_tiles = page_hi - page_lo + 1;
+
+  // ---- stage the queries (rows past the end repeat the last valid row; they are never written)
+  const size_t q_stride = (size_t)heads * QK;
+  {
+    const bf16* src = q + ((size_t)seq_q_start[seq] + q_first) * q_stride + (size_t)head * QK;
+    for (int idx = tid; idx < DP_BQ * CQ; idx += DP_THREADS) {
+      const int r = idx / CQ, c = idx % CQ;
+      const int rr = min(r, rows_valid - 1);
+      cp_async16(q_tile + tile_offset<QK>(r, c), src + (size_t)rr * q_stride + c * 8);
+    }
+  }
+  auto load_kv = [&](int t, int buf) {
+    const int page = pages[page_lo + t];
+    const bf16* ks = k_store + page_row(page, kvh, 0, kv_heads, QK);
+    const bf16* vs = v_store + page_row(page, kvh, 0, kv_heads, VD);
+    for (int idx = tid; idx < SB_PAGE_TOKENS * CQ; idx += DP_THREADS)
+      cp_async16(k_tiles + buf * K_BYTES + tile_offset<QK>(idx / CQ, idx % CQ), ks + (size_t)idx * 8);
+    for (int idx = tid; idx < SB_PAGE_TOKENS * CV; idx += DP_THREADS)
+      cp_async16(v_tiles + buf * V_BYTES + tile_offset<VD>(idx / CV, idx % CV), vs + (size_t)idx * 8);
+  };
+  load_kv(0, 0);
+  cp_commit();
+  if (n_tiles > 1) load_kv(1, 1);
+  cp_commit();
+  cp_wait<1>();
+  __syncthreads();
+
+  float o[2][NBLK][4];
+#pragma unroll
+  for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+    for (int n = 0; n < NBLK; ++n) o[mp][n][0] = o[mp][n][1] = o[mp][n][2] = o[mp][n][3] = 0.f;
+  float m_run[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l_run[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  const int row_a = warp * 16 + (lane >> 2);     // this thread's rows: row_a and row_a + 8
+  const int pos_a = pos0 + row_a, pos_b = pos_a + 8;
+  const int q_row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;   // the row this lane addresses for ldmatrix
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int buf = t & 1;
+    const uint8_t* kt = k_tiles + buf * K_BYTES;
+    const uint8_t* vt = v_tiles + buf * V_BYTES;
+    const int j0 = (page_lo + t) * SB_PAGE_TOKENS;
+    const bool edge = j0 + SB_PAGE_TOKENS - 1 > pos0 || (window > 0 && j0 <= pos0 + DP_BQ - window);
+    uint32_t pf[2][4][4];   // both maps' P as A fragments: 4 k-steps of 16 keys
+
+#pragma unroll
+    for (int mp = 0; mp < 2; ++mp) {
+      // S = Q_m K_m^T for 64 keys: 8 blocks of 8 keys
+      float s[8][4];
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const int step = mp * KSTEPS + kk;       // which 16 columns of the [k1 | k2] row
+        uint32_t qf[4];
+        ldmatrix_x4(smem_u32(q_tile + tile_offset<QK>(q_row, 2 * step + (lane >> 4))), qf[0], qf[1], qf[2], qf[3]);
+#pragma unroll
+        for (int nb = 0; nb < 8; nb += 2) {
+          uint32_t b0, b1, b2, b3;
+          const int key = nb * 8 + (lane & 7) + (lane >> 4) * 8;
+          ldmatrix_x4(smem_u32(kt + tile_offset<QK>(key, 2 * step + ((lane >> 3) & 1))), b0, b1, b2, b3);
+          mma_bf16(s[nb], qf, b0, b1);
+          mma_bf16(s[nb + 1], qf, b2, b3);
+        }
+      }
+      // scale, mask, online softmax of this map
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s[nb][e] * scale_log2;
+          if (edge) {
+            const int j = j0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+            const int p = (e & 2) ? pos_b : pos_a;
+            if (j > p || (window > 0 && j <= p - window)) v = -INFINITY;
+          }
+          s[nb][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m_run[mp][h], mx[h]);
+        m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+        alpha[h] = exp2f(m_run[mp][h] - m_use[h]);
+        m_run[mp][h] = m_new;
+      }
+      float rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) {
+        const float p0 = exp2f(s[nb][0] - m_use[0]), p1 = exp2f(s[nb][1] - m_use[0]);
+        const float p2 = exp2f(s[nb][2] - m_use[1]), p3 = exp2f(s[nb][3] - m_use[1]);
+        rs[0] += p0 + p1;
+        rs[1] += p2 + p3;
+        pf[mp][nb >> 1][(nb & 1) * 2] = pack_bf16(p0, p1);
+        pf[mp][nb >> 1][(nb & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) l_run[mp][h] = l_run[mp][h] * alpha[h] + rs[h];
+#pragma unroll
+      for (int n = 0; n < NBLK; ++n) {
+        o[mp][n][0] *= alpha[0]; o[mp][n][1] *= alpha[0];
+        o[mp][n][2] *= alpha[1]; o[mp][n][3] *= alpha[1];
+      }
+    }
+
+    // O_m += P_m V: a value fragment is read once and feeds both maps
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+      for (int n = 0; n < NBLK; n += 2) {
+        uint32_t b0, b1, b2, b3;
+        const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4_trans(smem_u32(vt + tile_offset<VD>(key, n + (lane >> 4))), b0, b1, b2, b3);
+        mma_bf16(o[0][n], pf[0][kk], b0, b1);
+        mma_bf16(o[0][n + 1], pf[0][kk], b2, b3);
+        mma_bf16(o[1][n], pf[1][kk], b0, b1);
+        mma_bf16(o[1][n + 1], pf[1][kk], b2, b3);
+      }
+    }
+
+    // this buffer is free: fetch the page after next, then make sure the next one has landed
+    __syncthreads();
+    if (t + 2 < n_tiles) load_kv(t + 2, buf);
+    cp_commit();
+    cp_wait<1>();
+    __syncthreads();
+  }
+  cp_wait<0>();
+
+  // ---- finish: both maps' row sums over the quad, the difference, its unit norm, the gate
+  float inv[2][2];
+#pragma unroll
+  for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float l = l_run[mp][h];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      inv[mp][h] = 1.f / l;
+    }
+  float ss[2] = {0.f, 0.f};
+#pragma unroll
+  for (int n = 0; n < NBLK; ++n) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int h = e >> 1;
+      const float d = o[0][n][e] * inv[0][h] - tail.lambda * (o[1][n][e] * inv[1][h]);
+      o[0][n][e] = d;
+      ss[h] += d * d;
+    }
+  }
+  float norm[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], 1);
+    ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], 2);
+    norm[h] = rsqrtf(ss[h] / (float)VD + tail.eps) * tail.out_scale;
+  }
+  const size_t o_stride = (size_t)heads * VD;
+  const size_t first_row = (size_t)seq_q_start[seq] + q_first;
+  bf16* dst = out + first_row * o_stride + (size_t)head * VD;
+  const bf16* gsrc = gate ? gate + first_row * gate_stride + (size_t)head * VD : nullptr;
+#pragma unroll
+  for (int n = 0; n < NBLK; ++n) {
+    const int col = n * 8 + (lane & 3) * 2;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = row_a + 8 * h;
+      if (row < rows_valid) {
+        float a = o[0][n][2 * h] * norm[h], b = o[0][n][2 * h + 1] * norm[h];
+        if (gsrc) {
+          const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(gsrc + (size_t)row * gate_stride + col);
+          a *= 1.f / (1.f + __expf(-__bfloat162float(g.x)));
+          b *= 1.f / (1.f + __expf(-__bfloat162float(g.y)));
+        }
+        *reinterpret_cast<uint32_t*>(dst + (size_t)row * o_stride + col) = pack_bf16(a, b);
+      }
+    }
+  }
+}
+
+template <int QK, int VD>
+static int launch(const void* q, const void* gate, int gate_stride, void* out, const void* k_store,
+                  const void* v_store, const int* block_table, int table_stride, const int* seq_slot,
+                  const int* seq_q_start, const int* seq_q_len, const int* seq_kv_len, const int* tile_seq,
+                  const int* tile_first, int n_tiles, int heads, int kv_heads, float scale, int window,
+                  DiffPrefillTail tail, cudaStream_t s) {
+  const int smem = DP_BQ * QK * 2 + 2 * SB_PAGE_TOKENS * (QK + VD) * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(diff_prefill_kernel<QK, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return launch_dependent(diff_prefill_kernel<QK, VD>, dim3(n_tiles, heads), dim3(DP_THREADS), smem, s,
+      (const bf16*)q, (const bf16*)gate, gate_stride, (bf16*)out, (const bf16*)k_store, (const bf16*)v_store,
+      block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len, tile_seq, tile_first, heads,
+      kv_heads, scale * 1.4426950408889634f, window, tail);
+}
+
+extern "C" {
+
+// 1 if the kernel is built for these sizes.
+int sb_diff_prefill_takes(int dim, int v_dim) {
+  return (dim == 16 || dim == 32 || dim == 64 || dim == 128) && (v_dim == 32 || v_dim == 64 || v_dim == 128) &&
+         !(dim == 128 && v_dim == 32);
+}
+
+// q [tokens, heads * 2 * dim] bfloat16 packed by sequence; gate null or rows of gate_stride elements
+// (even, 4-byte aligned) whose first heads * v_dim are the gate's pre-activations; out
+// [tokens, heads * v_dim].  The seq_* arrays and the work list of 64-query tiles as in the single-map
+// prompt kernel.  Returns -2 for sizes it is not built for.
+int sb_diff_prefill(const void* q, const void* gate, int gate_stride, void* out, const void* k_store,
+                    const void* v_store, const int* block_table, int table_stride, const int* seq_slot,
+                    const int* seq_q_start, const int* seq_q_len, const int* seq_kv_len, const int* tile_seq,
+                    const int* tile_first, int n_tiles, int heads, int kv_heads, int dim, int v_dim, float scale,
+                    int window, float lambda, float out_scale, float eps, cudaStream_t s) {
+  if (n_tiles == 0) return 0;
+  if (kv_heads <= 0 || heads % kv_heads || !sb_diff_prefill_takes(dim, v_dim)) return -2;
+  if (gate && ((gate_stride & 1) || ((uintptr_t)gate & 3))) return -2;
+  DiffPrefillTail tail = {lambda, out_scale, eps};
+#define ARGS q, gate, gate_stride, out, k_store, v_store, block_table, table_stride, seq_slot, seq_q_start, \
+             seq_q_len, seq_kv_len, tile_seq, tile_first, n_tiles, heads, kv_heads, scale, window, tail, s
+#define BY_V(QK) switch (v_dim) { case 32: return launch<QK, 32>(ARGS); case 64: return launch<QK, 64>(ARGS); \
+                                  case 128: return launch<QK, 128>(ARGS); default: return -2; }
+  switch (dim) {
+    case 16: BY_V(32)
+    case 32: BY_V(64)
+    case 64: BY_V(128)
+    case 128:
+      if (v_dim == 64) return launch<256, 64>(ARGS);
+      if (v_dim == 128) return launch<256, 128>(ARGS);
+      return -2;
+    default: return -2;
+  }
+#undef BY_V
+#undef ARGS
+}
+
+}  // extern "C"

@@ -47,6 +47,7 @@ SOURCES = (
     "sampling",
     "streams",
     "attention_diff",
+    "attention_diff_prefill",
 )
 
 _lock = threading.Lock()

@@ -845,8 +845,33 @@ DIFF_PREFILL_MIN_Q = 16
 
 
 def diff_prefill_takes(dtype, dim: int, v_dim: int) -> bool:
-    """Whether the tensor-core prompt kernel takes these sizes."""
-    return False
+    """Whether the tensor-core prompt kernel takes these sizes (csrc/attention_diff_prefill.cu)."""
+    return dtype == torch.bfloat16 and bool(_lib("attention_diff_prefill").sb_diff_prefill_takes(int(dim), int(v_dim)))
+
+
+def diff_attention_prefill(q, gate, k_store, v_store, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
+                           tile_seq, tile_first, heads, kv_heads, dim, v_dim, scale, lam, out_scale, eps,
+                           window=None):
+    """``diff_attention`` for steps with many tokens per sequence, on tensor cores (bfloat16): 64 queries
+    of a head a block, both maps in one pass over the pages.  ``q`` is packed by sequence; the ``seq_*``
+    arrays and the list of 64-query tiles are the step context's.  Sizes: see ``diff_prefill_takes``."""
+    gate_stride = _diff_check(q, gate, k_store, v_store, heads, kv_heads, dim, v_dim)
+    if not diff_prefill_takes(q.dtype, dim, v_dim):
+        raise KernelError(f"the tensor-core differential attention is not built for dim {dim}, v_dim {v_dim} in {q.dtype}")
+    if gate is not None and (gate_stride % 2 or gate.data_ptr() % 4):
+        raise KernelError("the gate's rows must start on 4-byte boundaries")
+    _need(block_table, "block_table", torch.int32, 2)
+    for name, t in (("seq_slot", seq_slot), ("seq_q_start", seq_q_start), ("seq_q_len", seq_q_len),
+                    ("seq_kv_len", seq_kv_len), ("tile_seq", tile_seq), ("tile_first", tile_first)):
+        _need(t, name, torch.int32, 1)
+    out = torch.empty((q.shape[0], heads * v_dim), dtype=q.dtype, device=q.device)
+    rc = _lib("attention_diff_prefill").sb_diff_prefill(
+        _ptr(q), _ptr(gate), int(gate_stride), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
+        block_table.shape[1], _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len),
+        _ptr(tile_seq), _ptr(tile_first), tile_seq.shape[0], heads, kv_heads, dim, v_dim, ctypes.c_float(scale),
+        int(window or 0), ctypes.c_float(lam), ctypes.c_float(out_scale), ctypes.c_float(eps), _stream())
+    _check(rc, "diff_attention_prefill")
+    return out
 
 
 def diff_prepare(proj, bias, heads, kv_heads, dim, v_dim, gate_width, temperature, tok_pos, tok_slot,
@@ -939,8 +964,8 @@ def diff_attention_step(q, gate, k_store, v_store, block_table, ctx, heads, kv_h
     brings many tokens run the bfloat16 tensor-core kernel (64 queries of a head a block); single
     tokens, short chunks, the 32-bit path and sizes that kernel refuses run one block per (row, head)
     whose warps share the keys."""
-    if (ctx.max_q_len >= DIFF_PREFILL_MIN_Q and ctx.host is not None
-            and diff_prefill_takes(q.dtype, dim, v_dim)):
+    if (ctx.max_q_len >= DIFF_PREFILL_MIN_Q and ctx.host is not None and diff_prefill_takes(q.dtype, dim, v_dim)
+            and (gate is None or (gate.stride(0) % 2 == 0 and gate.data_ptr() % 4 == 0))):
         return diff_attention_prefill(q, gate, k_store, v_store, block_table, ctx.seq_slot, ctx.seq_q_start,
                                       ctx.seq_q_len, ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first, heads,
                                       kv_heads, dim, v_dim, scale, lam, out_scale, eps, window)

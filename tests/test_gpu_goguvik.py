@@ -13,7 +13,7 @@ from tiny_goguvik import TINY_G, make_goguvik_folder
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = ["GA", "GB", "GC"]
+CONFIGS = ["GA", "GB", "GC", "GD"]
 TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 _cases, _runners = {}, {}
 
@@ -210,6 +210,57 @@ def test_attention_alone_with_one_key_that_stands_out(heads, groups, dim, vdim, 
     want = torch.cat([mean[h // (heads // groups)] for h in range(heads)])
     want = (want.view(heads, vdim) / want.view(heads, vdim).pow(2).mean(-1, keepdim=True).sqrt()).reshape(1, -1)
     close(got, want, dtype, "a window of three keys")
+
+
+@pytest.mark.parametrize("heads, groups, dim, vdim", [(4, 2, 16, 32), (2, 2, 32, 64), (3, 1, 64, 128), (2, 1, 128, 64),
+                                                      (2, 1, 16, 128), (2, 2, 128, 128)])
+def test_prompt_attention_on_tensor_cores_alone(heads, groups, dim, vdim):
+    """Ragged sequences in one launch: a prompt from position 0, a portion that starts in the middle
+    of a page behind 300 cached keys, a two-token portion; one key far back and one at the page
+    border are made to stand out; with and without a window."""
+    from starter_b200 import ops
+
+    t = torch.bfloat16
+    assert ops.diff_prefill_takes(t, dim, vdim)
+    pages = Pages(700, groups, dim, vdim, "bfloat16", seed=dim + vdim)
+    ks, vs, table = pages.store()
+    lam, lam0, eps, scale = 0.45, 0.2, 1e-6, 0.25
+    # (first position, count) per sequence; all read slot 1's pages, which is fine for reading
+    spans = [(0, 150), (300, 333), (698, 2), (63, 66)]
+    total = sum(n for _, n in spans)
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(total, heads, 2, dim, generator=g, dtype=torch.float64) * 0.3
+    for h in range(heads):
+        grp = h // (heads // groups)
+        q[:, h, 0] += 5.0 * pages.k[3, grp, 0] / scale / dim
+        q[:, h, 1] += 5.0 * pages.k[64, grp, 1] / scale / dim
+    gate = torch.randn(total, heads * vdim, generator=g, dtype=torch.float64)
+    qd = q.reshape(total, -1).to("cuda", t).contiguous()
+    gd = gate.to("cuda", t).contiguous()
+    qs, gs = qd.double().cpu().view(total, heads, 2, dim), gd.double().cpu()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")  # noqa: E731
+    starts, at = [], 0
+    for _, n in spans:
+        starts.append(at)
+        at += n
+    tiles = [(i, f) for i, (_, n) in enumerate(spans) for f in range(0, n, 64)]
+    for window in (None, 70):
+        got = ops.diff_attention_prefill(qd, gd, ks, vs, table, i32([1] * len(spans)), i32(starts),
+                                         i32([n for _, n in spans]), i32([p + n for p, n in spans]),
+                                         i32([i for i, _ in tiles]), i32([f for _, f in tiles]), heads, groups, dim,
+                                         vdim, scale, lam, 1 - lam0, eps, window)
+        for (p0, n), s0 in zip(spans, starts):
+            positions = torch.arange(p0, p0 + n)
+            want = torch.cat([plain.plain_differential_head(
+                qs[s0:s0 + n, h, 0], qs[s0:s0 + n, h, 1], pages.k[:, h // (heads // groups), 0],
+                pages.k[:, h // (heads // groups), 1], pages.v[:, h // (heads // groups)], scale, lam, lam0, eps,
+                positions, window) for h in range(heads)], -1) * torch.sigmoid(gs[s0:s0 + n])
+            close(got[s0:s0 + n], want, "bfloat16", f"positions {p0}..{p0 + n - 1}, window {window}", bf16=2.5e-2)
+        # the other kernel on the same rows agrees
+        pos = i32([p for p0, n in spans for p in range(p0, p0 + n)])
+        other = ops.diff_attention(qd, gd, ks, vs, table, i32([1] * total), pos, heads, groups, dim, vdim, scale, lam,
+                                   1 - lam0, eps, window=window, warps=2)
+        close(got, other, "bfloat16", f"both kernels, window {window}", bf16=2.5e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

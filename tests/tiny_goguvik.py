@@ -42,7 +42,15 @@ G_C = dict(architecture="Goguvik", vocab=300, width=80, streams=2, norm=dict(eps
     _layer(_mixer(6, 1, 24, 16, 0.15, 0.3, (0.3, 64), kv_from=0), 64),
 ])
 
-TINY_G = {"GA": G_A, "GB": G_B, "GC": G_C}
+# sizes the tensor-core prompt kernel takes (key rows of 32 and 64, value rows of 32 and 64), so that
+# whole prompts and portions run on it and single tokens on the other kernel, over the same cache
+G_D = dict(architecture="Goguvik", vocab=257, width=128, streams=2, norm=dict(eps=1e-6), layers=[
+    _layer(_mixer(4, 2, 16, 32, 0.25, 0.2, (0.4, 16)), 192),
+    _layer(_mixer(4, 2, 16, 32, 0.25, 0.2, (0.4, 16), kv_from=0), 192),
+    _layer(_mixer(2, 1, 32, 64, 0.18, 0.35, (0.4, 16)), 192),
+])
+
+TINY_G = {"GA": G_A, "GB": G_B, "GC": G_C, "GD": G_D}
 
 
 def make_goguvik_folder(tmp_path, name, seed=0, dtype=torch.float32):
