@@ -275,6 +275,234 @@ def workload(args) -> int:
     return 0
 
 
+#: sizes for ``--design goguvik``: layers that resemble a real model's (random weights).  Both designs get
+#: the same width, feed-forward, vocabulary, head counts, 128 key columns and 128 value columns per head.
+DESIGN_SIZES = {
+    "2048": dict(width=2048, ff=8192, heads=16, kv_heads=4, vocab=32768),
+    "2560": dict(width=2560, ff=9728, heads=32, kv_heads=8, vocab=151936),
+    "4096": dict(width=4096, ff=12288, heads=32, kv_heads=8, vocab=151936),
+}
+
+
+def goguvik_config(size: dict, layers: int) -> dict:
+    """Goguvik at ``size``: four streams, every second layer on the keys and values of the layer before."""
+    out = []
+    for i in range(layers):
+        mixer = dict(heads=size["heads"], kv_heads=size["kv_heads"], dim=64, vdim=128, scale=0.125, diff=0.3,
+                     q_temp=dict(coef=0.3, every=64))
+        if i % 2:
+            mixer["kv_from"] = i - 1
+        out.append(dict(type="attention", mixer=mixer, mlp=dict(kind="dense", ff=size["ff"])))
+    return dict(architecture="Goguvik", vocab=size["vocab"], width=size["width"], streams=4,
+                norm=dict(eps=1e-6), layers=out)
+
+
+def qwen3_config(size: dict, layers: int) -> dict:
+    return dict(QWEN3_4B, num_hidden_layers=layers, hidden_size=size["width"], intermediate_size=size["ff"],
+                num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=128,
+                vocab_size=size["vocab"])
+
+
+def design_compare(args) -> int:
+    """``--design goguvik``: prefill and decode throughput of Goguvik beside Qwen3 (the closest model
+    this library has) at equal sizes, and each design's own kernels alone against their rooflines.
+    Every number is timed on the device with CUDA events; the kernels alone run inside a CUDA graph,
+    once per layer on that layer's own weights and cache.  Prints one JSON line."""
+    import torch
+
+    from starter_b200 import ops
+    from starter_b200.config import config_from_dict
+    from starter_b200.engine import ModelRunner, StepEntry, random_model
+
+    pk = peaks()
+    layers = args.layers if args.layers_given else 8
+    batch, context, prompt_len = args.batch, 2048, PROMPT
+    warmup, steps = max(args.warmup, 3), max(min(args.steps, 64), 1)
+    sampler = ClockSampler()
+    sampler.start()
+    windows = []
+    gen = torch.Generator().manual_seed(0)
+    dev = torch.device("cuda:0")
+
+    def timed(fn, reps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.monotonic()
+        start.record()
+        for _ in range(reps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        windows.append((t0, time.monotonic()))
+        return start.elapsed_time(stop) / reps
+
+    def in_graph(calls):
+        """Microseconds per call of ``calls`` (one per layer), captured together and replayed."""
+        for c in calls:
+            c()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for c in calls:
+                c()
+        graph.replay()
+        return timed(graph.replay, 5) / len(calls) * 1e3
+
+    def kernels_alone(model, runner, design, size):
+        """Each design's own kernels, at the prompt's 2,048 rows and at the decode batch."""
+        spec = model.spec
+        blocks = [model.blocks[e.layer] for e in spec.schedule]
+        writers = [(b, e.cache) for b, e in zip(blocks, spec.schedule) if e.writes_cache]
+        cache = runner.cache
+        w, heads, kvh = size["width"], size["heads"], size["kv_heads"]
+        out = {}
+        slots = [runner.open_sequence() for _ in range(batch)]
+        for s in slots:
+            runner.step([StepEntry(s, torch.randint(0, spec.vocab_size, (context,), generator=gen).tolist(), [])])
+        for rows, name in ((prompt_len, "prompt"), (batch, "decode")):
+            if rows == prompt_len:
+                slot = runner.open_sequence()
+                ctx = runner.make_context([StepEntry(slot, [1] * prompt_len, [])])
+            else:
+                ctx = runner.make_context([StepEntry(s, [1], []) for s in slots])
+            x = (torch.randn(rows, w, device=dev) * 0.5).to(torch.bfloat16)
+            kv_tokens = int(ctx.host["seq_kv_len"].sum())
+            if design == "goguvik":
+                streams = torch.randn(rows, spec.streams, w, device=dev)
+                us = in_graph([lambda b=b: b.connection2.open(streams, ops_pending(b, x), b.norm2, torch.bfloat16) for b in blocks])
+                moved = rows * w * (2 * spec.streams * 4 + 2 + 2)
+                out[f"{name}: stream write + read + norm"] = dict(us=us, gbs=moved / us / 1e3)
+                m = blocks[0].mixer
+                proj = (torch.randn(rows, m.weight.shape[0], device=dev) * 0.5).to(torch.bfloat16)
+                q = (torch.randn(rows, m.q_size, device=dev) * 0.5).to(torch.bfloat16)
+                gate = proj[:, m.q_size:m.q_size + m.gate_size]
+                sp = m.spec
+
+                def prepare(b, e):
+                    k, v = cache.entry_pages(e)
+                    return ops.diff_prepare(proj, b.mixer.bias, heads, kvh, sp.head_dim, sp.value_dim, m.gate_size,
+                                            (0.3, 64), ctx.tok_pos, ctx.tok_slot, cache.block_table, k, v)
+
+                def attend(b, e):
+                    k, v = cache.entry_pages(e)
+                    return ops.diff_attention_step(q, gate, k, v, cache.block_table, ctx, heads, kvh, sp.head_dim,
+                                                   sp.value_dim, sp.scale, 0.4, 0.7, 1e-6)
+
+                us = in_graph([lambda b=b, e=e: prepare(b, e) for b, e in writers])
+                moved = rows * 2 * (2 * m.q_size + 2 * (m.k_size + m.v_size))
+                out[f"{name}: bias, temperature, cache write"] = dict(us=us, gbs=moved / us / 1e3)
+                us = in_graph([lambda b=b, e=e: attend(b, e) for b, e in writers])
+                flops = heads * (4 * sp.head_dim + 4 * sp.value_dim)
+            else:
+                res = x.clone()
+                us = in_graph([lambda b=b: ops.rmsnorm(res, b.norm1.weight, b.norm1.spec.eps, delta=x) for b in blocks])
+                out[f"{name}: residual sum + norm"] = dict(us=us, gbs=rows * w * 2 * 4 / us / 1e3)
+                m = blocks[0].mixer
+                sp = m.spec
+                qkv = (torch.randn(rows, m.qkv.shape[0], device=dev) * 0.5).to(torch.bfloat16)
+                rot = m.position.rotation()
+
+                def attend(b, e):
+                    k, v = cache.entry_pages(e)
+                    if rows == batch:
+                        return ops.attention_decode_qkv(qkv, k, v, cache.block_table, ctx.seq_slot, ctx.seq_kv_len, heads,
+                                                        kvh, sp.head_dim, sp.scale, None, b.mixer.q_norm, b.mixer.k_norm,
+                                                        sp.qk_norm_eps, rot.cos, rot.sin, write_cache=True,
+                                                        kv_hint=ctx.max_kv_len)
+                    qq = ops.qk_norm_rope_store(qkv, heads, kvh, sp.head_dim, b.mixer.q_norm, b.mixer.k_norm,
+                                                sp.qk_norm_eps, rot.cos, rot.sin, ctx.tok_pos, ctx.tok_slot,
+                                                cache.block_table, k, v)
+                    return ops.attention_prefill(qq, k, v, cache.block_table, ctx.seq_slot, ctx.seq_q_start,
+                                                 ctx.seq_q_len, ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first, heads, kvh,
+                                                 sp.head_dim, sp.scale, None, max_q_len=ctx.max_q_len,
+                                                 blocks=(ctx.block_seq, ctx.block_first))
+
+                if rows == prompt_len:
+                    def store(b, e):
+                        k, v = cache.entry_pages(e)
+                        return ops.qk_norm_rope_store(qkv, heads, kvh, sp.head_dim, b.mixer.q_norm, b.mixer.k_norm,
+                                                      sp.qk_norm_eps, rot.cos, rot.sin, ctx.tok_pos, ctx.tok_slot,
+                                                      cache.block_table, k, v)
+                    us_store = in_graph([lambda b=b, e=e: store(b, e) for b, e in writers])
+                    moved = rows * 2 * (qkv.shape[1] + heads * sp.head_dim + 2 * kvh * sp.head_dim)
+                    out[f"{name}: head norm, rotation, cache write"] = dict(us=us_store, gbs=moved / us_store / 1e3)
+                us = in_graph([lambda b=b, e=e: attend(b, e) for b, e in writers])
+                if rows == prompt_len:
+                    us -= us_store
+                flops = heads * 4 * sp.head_dim
+            if rows == prompt_len:
+                pairs = prompt_len * (prompt_len + 1) / 2
+                tf = flops * pairs / us / 1e6
+                out[f"{name}: attention"] = dict(us=us, tflops=tf, frac_of_bf16_peak=tf / pk["bf16_tflops"])
+                runner.close_sequence(slot)
+            else:
+                kv_bytes = cache.bytes_per_token() // len({e.cache for e in spec.schedule if e.writes_cache}) * kv_tokens
+                out[f"{name}: attention"] = dict(us=us, gbs=kv_bytes / us / 1e3, frac_of_copy_peak=kv_bytes / us / 1e3 / pk["hbm_gbs"])
+            for slot_, length in zip(ctx.host["seq_slot"].tolist(), ctx.host["seq_kv_len"].tolist()):
+                if rows == batch:
+                    cache.lengths[slot_] = length - 1       # the context made above counted a token that no step ran
+        for s in slots:
+            runner.close_sequence(s)
+        return {k: {a: round(b, 4 if "frac" in a else 1) for a, b in v.items()} for k, v in out.items()}
+
+    def ops_pending(block, y):
+        from starter_b200.parts import Pending
+        return Pending(y, block.connection1, block.mixer.deferred_bias)
+
+    results = {}
+    for size_name in (args.design_sizes.split(",") if args.design_sizes else list(DESIGN_SIZES)):
+        size = DESIGN_SIZES[size_name]
+        row = {"layers": layers}
+        for design, raw in (("goguvik", goguvik_config(size, layers)), ("qwen3", qwen3_config(size, layers))):
+            config = config_from_dict(raw)
+            model = random_model(config, seed=0, dtype="bfloat16")
+            vocab = model.spec.vocab_size
+            runner = ModelRunner(model, max_tokens=(batch + 1) * (context + 256) + prompt_len, max_sequences=batch + 2)
+            prompt = torch.randint(0, vocab, (prompt_len,), generator=gen).tolist()
+
+            def prefill_once():
+                slot = runner.open_sequence()
+                runner.step([StepEntry(slot, prompt, [prompt_len - 1])])
+                runner.close_sequence(slot)
+
+            for _ in range(warmup):
+                prefill_once()
+            prefill_ms = timed(prefill_once, 5)
+            slots = [runner.open_sequence() for _ in range(batch)]
+            for s in slots:
+                runner.reserve(s, context + 256)
+                runner.step([StepEntry(s, torch.randint(0, vocab, (context,), generator=gen).tolist(), [])])
+            entries = [StepEntry(s, [1], [0]) for s in slots]
+
+            def one():
+                runner.decode_tokens(entries, [0.0] * batch, [0] * batch)
+
+            for _ in range(warmup):
+                one()
+            decode_ms = timed(one, steps)
+            for s in slots:
+                runner.close_sequence(s)
+            runner.check_status()
+            step_bytes = model.step_weight_bytes() + runner.cache.bytes_per_token() * batch * context
+            row[design] = {
+                "prefill_tok_s": round(prompt_len / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+                "decode_tok_s": round(batch / decode_ms * 1e3, 1), "decode_ms_per_step": round(decode_ms, 4),
+                "decode_frac_of_copy_peak": round(step_bytes / (decode_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                "weight_mb_per_step": round(model.step_weight_bytes() / 1e6, 1),
+                "kernels": kernels_alone(model, runner, design, size),
+            }
+            del runner, model
+            torch.cuda.empty_cache()
+        results[size_name] = row
+    print(json.dumps({
+        "metric": "prefill tok/s at 2,048 tokens and decode tok/s at batch %d, context 2,048: Goguvik beside Qwen3 at "
+                  "equal sizes (BF16, random weights)" % batch,
+        "unit": "tok/s", "n_gpus": 1, "dtype": "bf16", "steps": steps, "warmup": warmup,
+        "data": "synthetic: random weights, uniform random token ids", "peaks": pk,
+        "sizes": {k: DESIGN_SIZES[k] for k in results}, "results": results, "clocks": sampler.stop(windows)}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -292,6 +520,10 @@ def main() -> int:
                              "generation range); the cache is sized for it")
     parser.add_argument("--per-stage", action="store_true",
                         help="also print where a decode step's time goes, kernel by kernel (stderr)")
+    parser.add_argument("--design", choices=["goguvik"], default=None,
+                        help="instead of the default run: that design beside Qwen3 at equal sizes (prefill, decode, "
+                             "and each design's own kernels against their rooflines)")
+    parser.add_argument("--design-sizes", default=None, help="comma-separated subset of " + ",".join(DESIGN_SIZES))
     args = parser.parse_args()
     args.layers_given = "--layers" in sys.argv
     if args.gpus != 1:
@@ -301,6 +533,8 @@ def main() -> int:
         return reference_arm(args)
     if args.workload:
         return workload(args)
+    if args.design:
+        return design_compare(args)
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
     decode_at = args.decode_at

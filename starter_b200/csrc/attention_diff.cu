@@ -16,8 +16,7 @@
 //                    1 + coef * ln(floor((p + 1) / every) + 1), files keys and values at each token's place
 //   diff_attention   one block per (token, head); its warps share the keys, merge, then finish the head
 //                    (any sizes, both types: single tokens, the 32-bit path, short chunks)
-//   diff_prefill     bfloat16 tensor-core kernel for steps with many tokens per sequence: 64 queries of
-//                    one head a block, both maps' scores by mma.sync, one pass over the keys
+// The bfloat16 tensor-core kernels for prompts and for single tokens are in attention_diff_prefill.cu.
 #include "common.cuh"
 
 #define SB_DIFF_MAX_I 8   // 2 * dim <= 256 and v_dim <= 256
@@ -65,6 +64,79 @@ __global__ void diff_prepare_kernel(const T* __restrict__ proj, int proj_stride,
     if (bias) v += bias[k0 + k_w + c];
     const int h = c / v_dim;
     v_store[page_row(page, h, off, kv_heads, v_dim) + (c - h * v_dim)] = from_f<T>(v);
+  }
+}
+
+// The same with eight consecutive columns a thread (16-byte accesses for bfloat16) and a row cut into
+// pieces (blockIdx.y): needs 2 * dim, v_dim, the gate's width and the row stride to be multiples of 8
+// and 16-byte aligned bases.
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* out) {
+  if (sizeof(T) == 2) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = to_f<T>(e[i]);
+  } else {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+  }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* v) {
+  if (sizeof(T) == 2) {
+    uint4 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) e[i] = from_f<T>(v[i]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  } else {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+template <typename T>
+__global__ void diff_prepare_vec_kernel(const T* __restrict__ proj, int proj_stride, const float* __restrict__ bias,
+                                        T* __restrict__ q_out, const int* __restrict__ tok_pos,
+                                        const int* __restrict__ tok_slot, const int* __restrict__ block_table,
+                                        int table_stride, T* __restrict__ k_store, T* __restrict__ v_store,
+                                        int heads, int kv_heads, int qk, int v_dim, int gate_width, float temp_coef,
+                                        int temp_every, int write_cache) {
+  const int q_w = heads * qk, k_w = kv_heads * qk, v_w = kv_heads * v_dim;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;      // column among [q | k | v]
+  const int src = c < q_w ? c : c + gate_width;                   // column of the stacked row
+  float bv[8];
+  const bool live = c < q_w + (write_cache ? k_w + v_w : 0);
+  if (live && bias) load8<float>(bias + src, bv);
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(proj);
+  SB_BEHIND_WAIT(tok_pos);
+  SB_BEHIND_WAIT(tok_slot);
+  if (!live) return;
+  const int token = blockIdx.x;
+  const int pos = tok_pos[token];
+  float v[8];
+  load8<T>(proj + (size_t)token * proj_stride + src, v);
+  if (c < q_w) {
+    float temp = 1.f;
+    if (temp_every > 0) temp = 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (bias ? rnd<T>(v[i] + bv[i]) : v[i]) * temp;
+    store8<T>(q_out + (size_t)token * q_w + c, v);
+    return;
+  }
+  if (bias) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] += bv[i];
+  }
+  const int page = block_table[(size_t)tok_slot[token] * table_stride + pos / SB_PAGE_TOKENS];
+  const int off = pos % SB_PAGE_TOKENS;
+  if (c < q_w + k_w) {
+    const int cc = c - q_w, h = cc / qk;
+    store8<T>(k_store + page_row(page, h, off, kv_heads, qk) + (cc - h * qk), v);
+  } else {
+    const int cc = c - q_w - k_w, h = cc / v_dim;
+    store8<T>(v_store + page_row(page, h, off, kv_heads, v_dim) + (cc - h * v_dim), v);
   }
 }
 
@@ -219,6 +291,21 @@ int sb_diff_prepare(int dtype, const void* proj, int proj_stride, const float* b
                     int gate_width, float temp_coef, int temp_every, int write_cache, cudaStream_t s) {
   if (n_tokens == 0) return 0;
   const int threads = 128;
+  const int qk = 2 * dim;
+  const uintptr_t all = (uintptr_t)proj | (uintptr_t)bias | (uintptr_t)q_out | (uintptr_t)k_store | (uintptr_t)v_store;
+  if (qk % 8 == 0 && v_dim % 8 == 0 && gate_width % 8 == 0 && proj_stride % 8 == 0 && (all & 15) == 0) {
+    const int cols = heads * qk + (write_cache ? kv_heads * (qk + v_dim) : 0);
+    const dim3 grid(n_tokens, (cols / 8 + threads - 1) / threads);
+    if (dtype == 0)
+      return launch_dependent(diff_prepare_vec_kernel<float>, grid, dim3(threads), 0, s, (const float*)proj,
+                              proj_stride, bias, (float*)q_out, tok_pos, tok_slot, block_table, table_stride,
+                              (float*)k_store, (float*)v_store, heads, kv_heads, qk, v_dim, gate_width,
+                              temp_coef, temp_every, write_cache);
+    return launch_dependent(diff_prepare_vec_kernel<bf16>, grid, dim3(threads), 0, s, (const bf16*)proj,
+                            proj_stride, bias, (bf16*)q_out, tok_pos, tok_slot, block_table, table_stride,
+                            (bf16*)k_store, (bf16*)v_store, heads, kv_heads, qk, v_dim, gate_width,
+                            temp_coef, temp_every, write_cache);
+  }
   if (dtype == 0)
     return launch_dependent(diff_prepare_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)proj,
                             proj_stride, bias, (float*)q_out, tok_pos, tok_slot, block_table, table_stride,

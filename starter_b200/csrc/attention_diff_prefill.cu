@@ -1,4 +1,5 @@
-// Differential attention for steps in which a sequence brings many tokens: bfloat16, tensor cores.
+// Differential attention on tensor cores (bfloat16): the kernel for steps in which a sequence brings
+// many tokens, and further down the one for single tokens.
 //
 // A block takes 64 queries of one query head (four warps of 16 rows) and walks the sequence's cache
 // pages once.  A page's key rows hold both maps, [k1 | k2] of `dim` each, so the two score tiles
@@ -275,6 +276,277 @@ diff_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate, i
   }
 }
 
+// ------------------------------------------------------------------------------------ single tokens
+//
+// One new token per sequence: the 16 MMA rows are the query heads that share a key/value head (more
+// than 16: chunks of 16), so a page's keys and values are read once for all of them and for both maps.
+// A block takes one (row, key/value head, part of the keys); its four warps share each page, 16 keys
+// a warp, through a three-stage cp.async ring; every warp keeps its own running maximum, sum and
+// accumulators per map, the warps' results meet in shared memory, and the block leaves its part as
+// (maximum, sum, accumulator) per head and map in scratch memory.  diff_decode_merge joins the parts
+// and finishes the head (difference, unit norm, gate).
+#define DD_STAGES 3
+
+template <int QK, int VD>
+__global__ void __launch_bounds__(DP_THREADS)
+diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store, const bf16* __restrict__ v_store,
+                   const int* __restrict__ block_table, int table_stride, const int* __restrict__ row_slot,
+                   const int* __restrict__ row_kv_len, int heads, int kv_heads, float scale_log2, int window,
+                   int n_splits, float* __restrict__ part) {
+  constexpr int CQ = QK / 8, CV = VD / 8;
+  constexpr int K_BYTES = SB_PAGE_TOKENS * QK * 2, V_BYTES = SB_PAGE_TOKENS * VD * 2;
+  constexpr int KSTEPS = QK / 32, NBLK = VD / 8, PER = VD + 2;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* q_tile = smem;                            // [16][QK]
+  uint8_t* k_tiles = smem + 16 * QK * 2;             // DD_STAGES x [64][QK]
+  uint8_t* v_tiles = k_tiles + DD_STAGES * K_BYTES;  // DD_STAGES x [64][VD]
+  float* meet = reinterpret_cast<float*>(k_tiles);   // after the walk: [4 warps][2 maps][16 rows][PER]
+
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(q);
+  SB_BEHIND_WAIT(k_store);
+  SB_BEHIND_WAIT(v_store);
+  SB_BEHIND_WAIT(row_slot);
+  SB_BEHIND_WAIT(row_kv_len);
+  const int group = heads / kv_heads, chunks = (group + 15) / 16;
+  const int split = blockIdx.x, kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks, row = blockIdx.z;
+  const int head0 = kvh * group + chunk * 16, n_heads = min(16, group - chunk * 16);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int pos = row_kv_len[row] - 1;
+  int lo = 0;
+  if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
+  const int page_lo = lo / SB_PAGE_TOKENS, page_hi = pos / SB_PAGE_TOKENS;
+  const int per = (page_hi - page_lo + n_splits) / n_splits;
+  const int p_begin = page_lo + split * per, p_end = min(page_hi + 1, p_begin + per);
+  const int n_pages = p_end - p_begin;
+  float* mine = part + (((size_t)row * heads + head0) * n_splits + split) * 2 * PER;   // + r * n_splits * 2 * PER per head
+  if (n_pages <= 0) {      // more parts than pages: this part is empty
+    for (int i = tid; i < n_heads * 2; i += DP_THREADS) {
+      float* dst = mine + (size_t)(i >> 1) * n_splits * 2 * PER + (i & 1) * PER;
+      dst[0] = -INFINITY;
+      dst[1] = 0.f;
+    }
+    return;
+  }
+  const int* pages = block_table + (size_t)row_slot[row] * table_stride;
+  {
+    const bf16* src = q + (size_t)row * heads * QK;
+    for (int idx = tid; idx < 16 * CQ; idx += DP_THREADS) {
+      const int r = idx / CQ, c = idx % CQ;
+      cp_async16(q_tile + tile_offset<QK>(r, c), src + (size_t)(head0 + min(r, n_heads - 1)) * QK + c * 8);
+    }
+  }
+  auto load_kv = [&](int t, int buf) {
+    const int page = pages[p_begin + t];
+    const bf16* ks = k_store + page_row(page, kvh, 0, kv_heads, QK);
+    const bf16* vs = v_store + page_row(page, kvh, 0, kv_heads, VD);
+    for (int idx = tid; idx < SB_PAGE_TOKENS * CQ; idx += DP_THREADS)
+      cp_async16(k_tiles + buf * K_BYTES + tile_offset<QK>(idx / CQ, idx % CQ), ks + (size_t)idx * 8);
+    for (int idx = tid; idx < SB_PAGE_TOKENS * CV; idx += DP_THREADS)
+      cp_async16(v_tiles + buf * V_BYTES + tile_offset<VD>(idx / CV, idx % CV), vs + (size_t)idx * 8);
+  };
+#pragma unroll
+  for (int s = 0; s < DD_STAGES - 1; ++s) {
+    if (s < n_pages) load_kv(s, s);
+    cp_commit();
+  }
+
+  float o[2][NBLK][4];
+#pragma unroll
+  for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+    for (int n = 0; n < NBLK; ++n) o[mp][n][0] = o[mp][n][1] = o[mp][n][2] = o[mp][n][3] = 0.f;
+  float m_run[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l_run[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  const int q_row = (lane & 7) + ((lane >> 3) & 1) * 8;
+
+  for (int t = 0; t < n_pages; ++t) {
+    cp_wait<DD_STAGES - 2>();
+    __syncthreads();                 // page t has landed for everyone, and everyone is done with page t - 1
+    if (t + DD_STAGES - 1 < n_pages) load_kv(t + DD_STAGES - 1, (t + DD_STAGES - 1) % DD_STAGES);
+    cp_commit();
+    const int buf = t % DD_STAGES;
+    const uint8_t* kt = k_tiles + buf * K_BYTES;
+    const uint8_t* vt = v_tiles + buf * V_BYTES;
+    const int j0 = (p_begin + t) * SB_PAGE_TOKENS + 16 * warp;      // this warp's 16 keys
+    if (j0 > pos || (window > 0 && j0 + 15 <= pos - window)) continue;   // none of them is seen
+    const bool edge = j0 + 15 > pos || (window > 0 && j0 <= pos - window);
+    uint32_t pf[2][4];
+#pragma unroll
+    for (int mp = 0; mp < 2; ++mp) {
+      float s[2][4];
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const int step = mp * KSTEPS + kk;
+        uint32_t qf[4], b0, b1, b2, b3;
+        ldmatrix_x4(smem_u32(q_tile + tile_offset<QK>(q_row, 2 * step + (lane >> 4))), qf[0], qf[1], qf[2], qf[3]);
+        const int key = 16 * warp + (lane & 7) + (lane >> 4) * 8;
+        ldmatrix_x4(smem_u32(kt + tile_offset<QK>(key, 2 * step + ((lane >> 3) & 1))), b0, b1, b2, b3);
+        mma_bf16(s[0], qf, b0, b1);
+        mma_bf16(s[1], qf, b2, b3);
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s[nb][e] * scale_log2;
+          if (edge) {
+            const int j = j0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+            if (j > pos || (window > 0 && j <= pos - window)) v = -INFINITY;
+          }
+          s[nb][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m_run[mp][h], mx[h]);
+        m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+        alpha[h] = exp2f(m_run[mp][h] - m_use[h]);
+        m_run[mp][h] = m_new;
+      }
+      float rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        const float p0 = exp2f(s[nb][0] - m_use[0]), p1 = exp2f(s[nb][1] - m_use[0]);
+        const float p2 = exp2f(s[nb][2] - m_use[1]), p3 = exp2f(s[nb][3] - m_use[1]);
+        rs[0] += p0 + p1;
+        rs[1] += p2 + p3;
+        pf[mp][nb * 2] = pack_bf16(p0, p1);
+        pf[mp][nb * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) l_run[mp][h] = l_run[mp][h] * alpha[h] + rs[h];
+#pragma unroll
+      for (int n = 0; n < NBLK; ++n) {
+        o[mp][n][0] *= alpha[0]; o[mp][n][1] *= alpha[0];
+        o[mp][n][2] *= alpha[1]; o[mp][n][3] *= alpha[1];
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < NBLK; n += 2) {
+      uint32_t b0, b1, b2, b3;
+      const int key = 16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4_trans(smem_u32(vt + tile_offset<VD>(key, n + (lane >> 4))), b0, b1, b2, b3);
+      mma_bf16(o[0][n], pf[0], b0, b1);
+      mma_bf16(o[0][n + 1], pf[0], b2, b3);
+      mma_bf16(o[1][n], pf[1], b0, b1);
+      mma_bf16(o[1][n + 1], pf[1], b2, b3);
+    }
+  }
+  cp_wait<0>();
+  __syncthreads();        // the ring is free: the warps' results meet in it
+
+#pragma unroll
+  for (int mp = 0; mp < 2; ++mp) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float l = l_run[mp][h];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      const int r = (lane >> 2) + 8 * h;
+      float* dst = meet + (((size_t)warp * 2 + mp) * 16 + r) * PER;
+      if ((lane & 3) == 0) { dst[0] = m_run[mp][h]; dst[1] = l; }
+#pragma unroll
+      for (int n = 0; n < NBLK; ++n) {
+        const int col = n * 8 + (lane & 3) * 2;
+        dst[2 + col] = o[mp][n][2 * h];
+        dst[2 + col + 1] = o[mp][n][2 * h + 1];
+      }
+    }
+  }
+  __syncthreads();
+  for (int item = tid; item < n_heads * 2 * PER; item += DP_THREADS) {
+    const int r = item / (2 * PER), rest = item % (2 * PER), mp = rest / PER, c = rest % PER;
+    float big = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) big = fmaxf(big, meet[(((size_t)w * 2 + mp) * 16 + r) * PER]);
+    float value;
+    if (c == 0) {
+      value = big;
+    } else {
+      value = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float* src = meet + (((size_t)w * 2 + mp) * 16 + r) * PER;
+        const float f = src[0] == -INFINITY ? 0.f : exp2f(src[0] - big);
+        value += src[c] * f;
+      }
+    }
+    mine[(size_t)r * n_splits * 2 * PER + mp * PER + c] = value;
+  }
+}
+
+// Joins the parts of one (row, head) and finishes the head.  part: [rows][heads][n_splits][2][v_dim + 2]
+// = (maximum in the base-2 domain, sum, accumulator) per map.
+__global__ void diff_decode_merge_kernel(const float* __restrict__ part, const bf16* __restrict__ gate, int gate_stride,
+                                         bf16* __restrict__ out, int heads, int v_dim, int n_splits,
+                                         DiffPrefillTail tail) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(part);
+  SB_BEHIND_WAIT(gate);
+  const int row = blockIdx.x / heads, head = blockIdx.x % heads;
+  const int per = v_dim + 2;
+  const float* src = part + ((size_t)row * heads + head) * n_splits * 2 * per;
+  float big[2] = {-INFINITY, -INFINITY};
+  for (int s = 0; s < n_splits; ++s) {
+    big[0] = fmaxf(big[0], src[(size_t)s * 2 * per]);
+    big[1] = fmaxf(big[1], src[(size_t)s * 2 * per + per]);
+  }
+  float den[2] = {0.f, 0.f};
+  for (int s = 0; s < n_splits; ++s)
+    for (int mp = 0; mp < 2; ++mp) {
+      const float m = src[(size_t)s * 2 * per + mp * per];
+      if (m != -INFINITY) den[mp] += src[(size_t)s * 2 * per + mp * per + 1] * exp2f(m - big[mp]);
+    }
+  float mine[2] = {0.f, 0.f};      // up to two columns a thread (v_dim <= 2 * blockDim)
+  float ss = 0.f;
+  for (int i = 0, c = threadIdx.x; c < v_dim; c += blockDim.x, ++i) {
+    float a[2] = {0.f, 0.f};
+    for (int s = 0; s < n_splits; ++s)
+      for (int mp = 0; mp < 2; ++mp) {
+        const float m = src[(size_t)s * 2 * per + mp * per];
+        if (m != -INFINITY) a[mp] += src[(size_t)s * 2 * per + mp * per + 2 + c] * exp2f(m - big[mp]);
+      }
+    const float d = a[0] / den[0] - tail.lambda * (a[1] / den[1]);
+    if (i < 2) mine[i] = d;
+    ss += d * d;
+  }
+  ss = block_sum(ss, scratch);
+  const float norm = rsqrtf(ss / (float)v_dim + tail.eps) * tail.out_scale;
+  for (int i = 0, c = threadIdx.x; c < v_dim; c += blockDim.x, ++i) {
+    float v = mine[i] * norm;
+    if (gate) v *= 1.f / (1.f + __expf(-__bfloat162float(gate[(size_t)row * gate_stride + (size_t)head * v_dim + c])));
+    out[((size_t)row * heads + head) * v_dim + c] = __float2bfloat16_rn(v);
+  }
+}
+
+template <int QK, int VD>
+static int launch_decode(const void* q, const void* k_store, const void* v_store, const int* block_table,
+                         int table_stride, const int* row_slot, const int* row_kv_len, int rows, int heads,
+                         int kv_heads, float scale, int window, int n_splits, float* part, cudaStream_t s) {
+  constexpr int ring = DD_STAGES * SB_PAGE_TOKENS * (QK + VD) * 2, meeting = 4 * 2 * 16 * (VD + 2) * 4;
+  const int smem = 16 * QK * 2 + (ring > meeting ? ring : meeting);     // the meeting area lies over the ring
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(diff_decode_kernel<QK, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int chunks = (heads / kv_heads + 15) / 16;
+  return launch_dependent(diff_decode_kernel<QK, VD>, dim3(n_splits, kv_heads * chunks, rows), dim3(DP_THREADS), smem, s,
+      (const bf16*)q, (const bf16*)k_store, (const bf16*)v_store, block_table, table_stride, row_slot, row_kv_len,
+      heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part);
+}
+
 template <int QK, int VD>
 static int launch(const void* q, const void* gate, int gate_stride, void* out, const void* k_store,
                   const void* v_store, const int* block_table, int table_stride, const int* seq_slot,
@@ -331,6 +603,41 @@ int sb_diff_prefill(const void* q, const void* gate, int gate_stride, void* out,
   }
 #undef BY_V
 #undef ARGS
+}
+
+// One query row per sequence (its newest token, already in the cache): q [rows, heads * 2 * dim], out
+// [rows, heads * v_dim]; row_kv_len[r] counts the row's own key.  part: float scratch of
+// rows * heads * n_splits * 2 * (v_dim + 2).  Two launches (the walk, the merge).  v_dim <= 256.
+int sb_diff_decode(const void* q, const void* gate, int gate_stride, void* out, const void* k_store,
+                   const void* v_store, const int* block_table, int table_stride, const int* row_slot,
+                   const int* row_kv_len, int rows, int heads, int kv_heads, int dim, int v_dim, float scale,
+                   int window, float lambda, float out_scale, float eps, int n_splits, float* part,
+                   cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (kv_heads <= 0 || heads % kv_heads || !sb_diff_prefill_takes(dim, v_dim) || n_splits < 1 || n_splits > 65535) return -2;
+  int rc = -2;
+#define ARGS q, k_store, v_store, block_table, table_stride, row_slot, row_kv_len, rows, heads, kv_heads, scale, window, \
+             n_splits, part, s
+#define BY_V(QK) switch (v_dim) { case 32: rc = launch_decode<QK, 32>(ARGS); break; case 64: rc = launch_decode<QK, 64>(ARGS); break; \
+                                  case 128: rc = launch_decode<QK, 128>(ARGS); break; default: return -2; } break;
+  switch (dim) {
+    case 16: BY_V(32)
+    case 32: BY_V(64)
+    case 64: BY_V(128)
+    case 128:
+      if (v_dim == 64) rc = launch_decode<256, 64>(ARGS);
+      else if (v_dim == 128) rc = launch_decode<256, 128>(ARGS);
+      else return -2;
+      break;
+    default: return -2;
+  }
+#undef BY_V
+#undef ARGS
+  if (rc != 0) return rc;
+  DiffPrefillTail tail = {lambda, out_scale, eps};
+  const int threads = v_dim >= 128 ? 128 : 64;
+  return launch_dependent(diff_decode_merge_kernel, dim3(rows * heads), dim3(threads), 0, s, (const float*)part,
+                          (const bf16*)gate, gate_stride, (bf16*)out, heads, v_dim, n_splits, tail);
 }
 
 }  // extern "C"

@@ -40,58 +40,103 @@ __global__ void embed_streams_kernel(const int* __restrict__ tokens, const T* __
   }
 }
 
-// norm_kind 0: normed = u (rounded to T); 1: Dynamic Tanh of u.
-template <typename T, int S>
+// V consecutive values of T as floats and back (V = 4: one 8- or 16-byte access; V = 1: any address).
+template <typename T, int V> __device__ __forceinline__ void load_v(const T* p, float* out) {
+  if (V == 4 && sizeof(T) == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  } else if (V == 4) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) out[i] = to_f<T>(e[i]);
+  } else {
+    out[0] = to_f<T>(p[0]);
+  }
+}
+template <typename T, int V> __device__ __forceinline__ void store_v(T* p, const float* v) {
+  if (V == 4 && sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  } else if (V == 4) {
+    uint2 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[i] = from_f<T>(v[i]);
+    *reinterpret_cast<uint2*>(p) = raw;
+  } else {
+    p[0] = from_f<T>(v[0]);
+  }
+}
+
+// norm_kind 0: normed = u (rounded to T); 1: Dynamic Tanh of u.  Nothing here sums over a row, so a row
+// is cut into pieces of blockDim * V columns (blockIdx.y) and a thread owns V consecutive columns.
+template <typename T, int S, int V>
 __global__ void hyper_step_kernel(float* __restrict__ streams, const T* __restrict__ y,
                                   const float* __restrict__ y_bias, const float* __restrict__ mix_prev,
                                   const float* __restrict__ out_prev, const float* __restrict__ in_next,
                                   int norm_kind, const float* __restrict__ alpha_p,
                                   const float* __restrict__ w, const float* __restrict__ b,
                                   T* __restrict__ normed, const int* __restrict__ rows, int hidden) {
-  __shared__ float s_mix[S * S], s_out[S], s_in[S];
-  if (threadIdx.x < S * S) s_mix[threadIdx.x] = y ? mix_prev[threadIdx.x] : 0.f;
-  if (threadIdx.x < S) {
-    s_out[threadIdx.x] = y ? out_prev[threadIdx.x] : 0.f;
-    s_in[threadIdx.x] = in_next ? in_next[threadIdx.x] : 1.f;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+  float mix[S * S], outw[S], inw[S];
+#pragma unroll
+  for (int i = 0; i < S * S; ++i) mix[i] = y ? mix_prev[i] : 0.f;
+#pragma unroll
+  for (int i = 0; i < S; ++i) {
+    outw[i] = y ? out_prev[i] : 0.f;
+    inw[i] = in_next ? in_next[i] : 1.f;
   }
   const float alpha = norm_kind == 1 ? alpha_p[0] : 0.f;
+  float wv[V], bv[V], biasv[V];
+  if (c < hidden) {
+    if (norm_kind == 1) { load_v<float, V>(w + c, wv); load_v<float, V>(b + c, bv); }
+    if (y && y_bias) load_v<float, V>(y_bias + c, biasv);
+  }
   pdl_trigger();
   pdl_wait();
   SB_BEHIND_WAIT(y);
   SB_BEHIND_WAIT(rows);
-  __syncthreads();
+  if (c >= hidden) return;
   const int out_row = blockIdx.x;
   const int in_row = rows ? rows[out_row] : out_row;
-  float* xr = streams + (size_t)in_row * S * hidden;
-  const T* yr = y ? y + (size_t)in_row * hidden : nullptr;
-  T* nr = normed + (size_t)out_row * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-    float x[S];
+  float* xr = streams + (size_t)in_row * S * hidden + c;
+  float x[S][V];
 #pragma unroll
-    for (int s = 0; s < S; ++s) x[s] = xr[(size_t)s * hidden + c];
-    if (yr) {
-      float yv = to_f<T>(yr[c]);
-      if (y_bias) yv += y_bias[c];
-      float nx[S];
+  for (int s = 0; s < S; ++s) load_v<float, V>(xr + (size_t)s * hidden, x[s]);
+  if (y) {
+    float yv[V];
+    load_v<T, V>(y + (size_t)in_row * hidden + c, yv);
+    if (y_bias) {
 #pragma unroll
-      for (int t = 0; t < S; ++t) {
+      for (int i = 0; i < V; ++i) yv[i] += biasv[i];
+    }
+    float nx[S][V];
+#pragma unroll
+    for (int t = 0; t < S; ++t) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
         float a = 0.f;
 #pragma unroll
-        for (int s = 0; s < S; ++s) a += s_mix[s * S + t] * x[s];
-        nx[t] = a + s_out[t] * yv;
-      }
-#pragma unroll
-      for (int t = 0; t < S; ++t) {
-        x[t] = nx[t];
-        if (!rows) xr[(size_t)t * hidden + c] = nx[t];
+        for (int s = 0; s < S; ++s) a += mix[s * S + t] * x[s][i];
+        nx[t][i] = a + outw[t] * yv[i];
       }
     }
-    float u = 0.f;
 #pragma unroll
-    for (int s = 0; s < S; ++s) u += s_in[s] * x[s];
-    if (norm_kind == 1) u = tanhf(alpha * u) * w[c] + b[c];
-    nr[c] = from_f<T>(u);
+    for (int t = 0; t < S; ++t) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) x[t][i] = nx[t][i];
+      if (!rows) store_v<float, V>(xr + (size_t)t * hidden, nx[t]);
+    }
   }
+  float u[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    float a = 0.f;
+#pragma unroll
+    for (int s = 0; s < S; ++s) a += inw[s] * x[s][i];
+    u[i] = norm_kind == 1 ? tanhf(alpha * a) * wv[i] + bv[i] : a;
+  }
+  store_v<T, V>(normed + (size_t)out_row * hidden + c, u);
 }
 
 // Dynamic Tanh on a single stream of the working type, with the residual sum in front of it as the
@@ -130,19 +175,31 @@ __global__ void add_bias_kernel(T* __restrict__ y, const float* __restrict__ bia
   for (; i < total; i += stride) y[i] = from_f<T>(to_f<T>(y[i]) + bias[i % width]);
 }
 
-template <typename T>
-static int launch_step(int S, float* streams, const void* y, const float* y_bias, const float* mix_prev,
-                       const float* out_prev, const float* in_next, int norm_kind, const float* alpha,
-                       const float* w, const float* b, void* normed, const int* rows, int n_rows, int hidden,
-                       cudaStream_t s) {
-  const int threads = hidden >= 1024 ? 256 : 128;
-#define GO(N) case N: return launch_dependent(hyper_step_kernel<T, N>, dim3(n_rows), dim3(threads), 0, s, streams, \
+template <typename T, int V>
+static int launch_step_v(int S, float* streams, const void* y, const float* y_bias, const float* mix_prev,
+                         const float* out_prev, const float* in_next, int norm_kind, const float* alpha,
+                         const float* w, const float* b, void* normed, const int* rows, int n_rows, int hidden,
+                         cudaStream_t s) {
+  const int threads = 128;
+  const dim3 grid(n_rows, (hidden + threads * V - 1) / (threads * V));
+#define GO(N) case N: return launch_dependent(hyper_step_kernel<T, N, V>, grid, dim3(threads), 0, s, streams, \
     (const T*)y, y_bias, mix_prev, out_prev, in_next, norm_kind, alpha, w, b, (T*)normed, rows, hidden)
   switch (S) {
     GO(1); GO(2); GO(3); GO(4); GO(5); GO(6); GO(7); GO(8);
   }
 #undef GO
   return -2;
+}
+
+template <typename T>
+static int launch_step(int S, float* streams, const void* y, const float* y_bias, const float* mix_prev,
+                       const float* out_prev, const float* in_next, int norm_kind, const float* alpha,
+                       const float* w, const float* b, void* normed, const int* rows, int n_rows, int hidden,
+                       cudaStream_t s) {
+  const uintptr_t all = (uintptr_t)streams | (uintptr_t)y | (uintptr_t)y_bias | (uintptr_t)w | (uintptr_t)b | (uintptr_t)normed;
+  if (hidden % 4 == 0 && (all & 15) == 0)
+    return launch_step_v<T, 4>(S, streams, y, y_bias, mix_prev, out_prev, in_next, norm_kind, alpha, w, b, normed, rows, n_rows, hidden, s);
+  return launch_step_v<T, 1>(S, streams, y, y_bias, mix_prev, out_prev, in_next, norm_kind, alpha, w, b, normed, rows, n_rows, hidden, s);
 }
 
 extern "C" {

@@ -958,17 +958,51 @@ def diff_attention(q, gate, k_store, v_store, block_table, tok_slot, tok_pos, he
     return out
 
 
+def diff_attention_decode(q, gate, k_store, v_store, block_table, row_slot, row_kv_len, heads, kv_heads, dim, v_dim,
+                          scale, lam, out_scale, eps, window=None, n_splits=None, kv_hint=0):
+    """``diff_attention`` for one new token per sequence, on tensor cores (bfloat16): the query heads
+    of a key/value head are the MMA's rows, so a page is read once for all of them and both maps;
+    each row's keys are cut into ``n_splits`` parts (chosen from ``kv_hint``, the longest sequence,
+    so that the blocks fill the GPU) that a second kernel joins.  Row ``i`` is the newest token of the
+    sequence in ``row_slot[i]``, already in the cache; ``row_kv_len[i]`` counts it."""
+    gate_stride = _diff_check(q, gate, k_store, v_store, heads, kv_heads, dim, v_dim)
+    if not diff_prefill_takes(q.dtype, dim, v_dim):
+        raise KernelError(f"the tensor-core differential attention is not built for dim {dim}, v_dim {v_dim} in {q.dtype}")
+    _need(block_table, "block_table", torch.int32, 2)
+    _need(row_slot, "row_slot", torch.int32, 1)
+    _need(row_kv_len, "row_kv_len", torch.int32, 1)
+    rows = q.shape[0]
+    if n_splits is None:
+        blocks = rows * kv_heads * (-(-(heads // kv_heads) // 16))
+        pages = max(1, -(-kv_hint // PAGE_TOKENS))
+        n_splits = max(1, min(pages, (2 * 148) // max(blocks, 1), 64))
+    out = torch.empty((rows, heads * v_dim), dtype=q.dtype, device=q.device)
+    part = torch.empty((rows * heads * n_splits * 2 * (v_dim + 2),), dtype=torch.float32, device=q.device)
+    rc = _lib("attention_diff_prefill").sb_diff_decode(
+        _ptr(q), _ptr(gate), int(gate_stride), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
+        block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, dim, v_dim,
+        ctypes.c_float(scale), int(window or 0), ctypes.c_float(lam), ctypes.c_float(out_scale), ctypes.c_float(eps),
+        int(n_splits), _ptr(part), _stream())
+    _check(rc, "diff_attention_decode", 2)
+    return out
+
+
 def diff_attention_step(q, gate, k_store, v_store, block_table, ctx, heads, kv_heads, dim, v_dim, scale, lam,
                         out_scale, eps, window=None):
     """The differential attention of one step, by the kernel that suits it: steps in which a sequence
-    brings many tokens run the bfloat16 tensor-core kernel (64 queries of a head a block); single
-    tokens, short chunks, the 32-bit path and sizes that kernel refuses run one block per (row, head)
-    whose warps share the keys."""
+    brings many tokens run the bfloat16 tensor-core kernel (64 queries of a head a block); steps of
+    single tokens the tensor-core kernel whose rows are the heads of a key/value head; short chunks,
+    the 32-bit path and sizes those kernels are not built for run one block per (row, head) whose warps
+    share the keys."""
     if (ctx.max_q_len >= DIFF_PREFILL_MIN_Q and ctx.host is not None and diff_prefill_takes(q.dtype, dim, v_dim)
             and (gate is None or (gate.stride(0) % 2 == 0 and gate.data_ptr() % 4 == 0))):
         return diff_attention_prefill(q, gate, k_store, v_store, block_table, ctx.seq_slot, ctx.seq_q_start,
                                       ctx.seq_q_len, ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first, heads,
                                       kv_heads, dim, v_dim, scale, lam, out_scale, eps, window)
+    if ctx.max_q_len == 1 and diff_prefill_takes(q.dtype, dim, v_dim):
+        return diff_attention_decode(q, gate, k_store, v_store, block_table, ctx.seq_slot, ctx.seq_kv_len, heads,
+                                     kv_heads, dim, v_dim, scale, lam, out_scale, eps, window,
+                                     kv_hint=ctx.max_kv_len)
     return diff_attention(q, gate, k_store, v_store, block_table, ctx.tok_slot, ctx.tok_pos, heads, kv_heads,
                           dim, v_dim, scale, lam, out_scale, eps, window, kv_hint=ctx.max_kv_len)
 

@@ -67,8 +67,9 @@ def test_dynamic_tanh_alone(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [40, 37, 600])
 @pytest.mark.parametrize("streams", [1, 2, 3, 4, 5, 8])
-def test_stream_step_alone(streams, dtype):
+def test_stream_step_alone(streams, hidden, dtype):
     """The pending write, the next read and the norm in one kernel; the matrix is [from, to], every
     stream is formed from the OLD ones, and selected rows leave the streams as they were."""
     from starter_b200 import ops
@@ -76,9 +77,9 @@ def test_stream_step_alone(streams, dtype):
     t = TORCH[dtype]
     g = torch.Generator().manual_seed(10 + streams)
     rnd = lambda *shape: torch.randn(*shape, generator=g, dtype=torch.float64)  # noqa: E731
-    x, y = rnd(7, streams, 40), rnd(7, 40)
-    mix, out, read, bias = rnd(streams, streams), rnd(streams), rnd(streams), rnd(40)
-    alpha, w, b = torch.tensor(0.4, dtype=torch.float64), rnd(40), rnd(40)
+    x, y = rnd(7, streams, hidden), rnd(7, hidden)
+    mix, out, read, bias = rnd(streams, streams), rnd(streams), rnd(streams), rnd(hidden)
+    alpha, w, b = torch.tensor(0.4, dtype=torch.float64), rnd(hidden), rnd(hidden)
     dev = lambda v, ty=torch.float32: v.to("cuda", ty).contiguous()  # noqa: E731
     xd, yd = dev(x), dev(y, t)
     y_seen = yd.double().cpu()
@@ -263,14 +264,50 @@ def test_prompt_attention_on_tensor_cores_alone(heads, groups, dim, vdim):
         close(got, other, "bfloat16", f"both kernels, window {window}", bf16=2.5e-2)
 
 
+@pytest.mark.parametrize("heads, groups, dim, vdim", [(4, 2, 16, 32), (2, 2, 32, 64), (8, 2, 64, 128), (2, 1, 128, 64),
+                                                      (40, 2, 16, 128), (2, 2, 128, 128)])
+def test_single_token_attention_on_tensor_cores_alone(heads, groups, dim, vdim):
+    """Rows of unequal lengths in one launch (1 key, a page less one, a page, a page and one, 700),
+    every number of parts from one to more than there are pages, a key far back and the newest made
+    to stand out, with and without a window; 20 heads on one key/value head take two chunks of rows."""
+    from starter_b200 import ops
+
+    t = torch.bfloat16
+    pages = Pages(700, groups, dim, vdim, "bfloat16", seed=3 * dim + vdim)
+    ks, vs, table = pages.store()
+    lam, lam0, eps, scale = 0.6, 0.25, 1e-6, 0.3
+    lengths = [1, 63, 64, 65, 700, 130]
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(len(lengths), heads, 2, dim, generator=g, dtype=torch.float64) * 0.3
+    for h in range(heads):
+        grp = h // (heads // groups)
+        q[:, h, 0] += 5.0 * pages.k[1, grp, 0] / scale / dim
+        for r, n in enumerate(lengths):
+            q[r, h, 1] += 5.0 * pages.k[n - 1, grp, 1] / scale / dim
+    gate = torch.randn(len(lengths), heads * vdim, generator=g, dtype=torch.float64)
+    qd, gd = q.reshape(len(lengths), -1).to("cuda", t).contiguous(), gate.to("cuda", t).contiguous()
+    qs, gs = qd.double().cpu().view(len(lengths), heads, 2, dim), gd.double().cpu()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")  # noqa: E731
+    for window in (None, 70):
+        want = torch.stack([torch.cat([plain.plain_differential_head(
+            qs[r:r + 1, h, 0], qs[r:r + 1, h, 1], pages.k[:, h // (heads // groups), 0], pages.k[:, h // (heads // groups), 1],
+            pages.v[:, h // (heads // groups)], scale, lam, lam0, eps, torch.tensor([n - 1]), window)[0]
+            for h in range(heads)]) for r, n in enumerate(lengths)]) * torch.sigmoid(gs)
+        for splits in (1, 2, 3, 11, 16, None):
+            got = ops.diff_attention_decode(qd, gd, ks, vs, table, i32([1] * len(lengths)), i32(lengths), heads, groups,
+                                            dim, vdim, scale, lam, 1 - lam0, eps, window, n_splits=splits, kv_hint=700)
+            close(got, want, "bfloat16", f"{splits} parts, window {window}", bf16=2.5e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_prepare_alone(dtype):
+@pytest.mark.parametrize("vdim", [12, 16])
+def test_prepare_alone(vdim, dtype):
     """Biases, the temperature on both sides of every step of its quotient, and keys and values filed
     at their own places across a page border."""
     from starter_b200 import ops
 
     t = TORCH[dtype]
-    heads, groups, dim, vdim, every, coef = 3, 1, 8, 12, 8, 0.75
+    heads, groups, dim, every, coef = 3, 1, 8, 8, 0.75      # value rows of 12 take the plain kernel, of 16 the vector one
     gate_w = heads * vdim
     width = heads * 2 * dim + gate_w + groups * (2 * dim + vdim)
     positions = [0, 6, 7, 8, 14, 15, 16, 62, 63, 64, 65, 127, 128]
