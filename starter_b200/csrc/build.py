@@ -48,6 +48,7 @@ SOURCES = (
     "streams",
     "attention_diff",
     "attention_diff_prefill",
+    "attention_diff_prefill_tc",
 )
 
 _lock = threading.Lock()

@@ -849,22 +849,50 @@ def diff_prefill_takes(dtype, dim: int, v_dim: int) -> bool:
     return dtype == torch.bfloat16 and bool(_lib("attention_diff_prefill").sb_diff_prefill_takes(int(dim), int(v_dim)))
 
 
+def diff_prefill_tc_takes(dtype, dim: int, v_dim: int) -> bool:
+    """Whether the tcgen05 prompt kernel takes these sizes (csrc/attention_diff_prefill_tc.cu)."""
+    return dtype == torch.bfloat16 and bool(_lib("attention_diff_prefill_tc").sb_diff_prefill_tc_takes(int(dim), int(v_dim)))
+
+
 def diff_attention_prefill(q, gate, k_store, v_store, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
                            tile_seq, tile_first, heads, kv_heads, dim, v_dim, scale, lam, out_scale, eps,
-                           window=None):
-    """``diff_attention`` for steps with many tokens per sequence, on tensor cores (bfloat16): 64 queries
-    of a head a block, both maps in one pass over the pages.  ``q`` is packed by sequence; the ``seq_*``
-    arrays and the list of 64-query tiles are the step context's.  Sizes: see ``diff_prefill_takes``."""
+                           window=None, status=None, kernel=None, max_q_len=None):
+    """``diff_attention`` for steps with many tokens per sequence, on tensor cores (bfloat16), both maps
+    in one pass over the pages.  ``q`` is packed by sequence; the ``seq_*`` arrays and the list of
+    64-query tiles are the step context's.  With ``dim`` 64 and ``v_dim`` 64 or 128 and a sequence that
+    brings at least 128 tokens (``max_q_len``, taken as large when not given) the tcgen05 kernel runs
+    (128 queries of a head a block, scores and outputs of both maps in tensor memory); otherwise the
+    mma.sync kernel (64 queries a block; sizes: ``diff_prefill_takes``).  ``kernel`` ("tcgen05" or
+    "mma") forces one.  ``status``: the device word in which the tcgen05 kernel reports a wait that
+    ran out (bit 16)."""
     gate_stride = _diff_check(q, gate, k_store, v_store, heads, kv_heads, dim, v_dim)
-    if not diff_prefill_takes(q.dtype, dim, v_dim):
-        raise KernelError(f"the tensor-core differential attention is not built for dim {dim}, v_dim {v_dim} in {q.dtype}")
-    if gate is not None and (gate_stride % 2 or gate.data_ptr() % 4):
-        raise KernelError("the gate's rows must start on 4-byte boundaries")
     _need(block_table, "block_table", torch.int32, 2)
     for name, t in (("seq_slot", seq_slot), ("seq_q_start", seq_q_start), ("seq_q_len", seq_q_len),
                     ("seq_kv_len", seq_kv_len), ("tile_seq", tile_seq), ("tile_first", tile_first)):
         _need(t, name, torch.int32, 1)
+    tc_ok = (diff_prefill_tc_takes(q.dtype, dim, v_dim) and q.data_ptr() % 16 == 0
+             and (gate is None or (gate_stride % 8 == 0 and gate.data_ptr() % 16 == 0)))
+    if kernel is None:
+        kernel = "tcgen05" if tc_ok and (max_q_len is None or max_q_len >= 128) else "mma"
     out = torch.empty((q.shape[0], heads * v_dim), dtype=q.dtype, device=q.device)
+    if kernel == "tcgen05":
+        if not tc_ok:
+            raise KernelError(f"the tcgen05 differential attention takes dim 64 and v_dim 64 or 128 in bfloat16 with "
+                              f"16-byte aligned rows; got dim {dim}, v_dim {v_dim}, {q.dtype}")
+        rc = _lib("attention_diff_prefill_tc").sb_diff_prefill_tc(
+            _ptr(q), _ptr(gate), int(gate_stride), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
+            block_table.shape[1], _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len),
+            _ptr(tile_seq), _ptr(tile_first), tile_seq.shape[0], q.shape[0], k_store.shape[0], heads, kv_heads, dim,
+            v_dim, ctypes.c_float(scale), int(window or 0), ctypes.c_float(lam), ctypes.c_float(out_scale),
+            ctypes.c_float(eps), _ptr(status), _stream())
+        if rc in (-3, -4):
+            raise KernelError(f"the TMA descriptors for the differential attention could not be made (code {rc})")
+        _check(rc, "diff_attention_prefill_tc")
+        return out
+    if not diff_prefill_takes(q.dtype, dim, v_dim):
+        raise KernelError(f"the tensor-core differential attention is not built for dim {dim}, v_dim {v_dim} in {q.dtype}")
+    if gate is not None and (gate_stride % 2 or gate.data_ptr() % 4):
+        raise KernelError("the gate's rows must start on 4-byte boundaries")
     rc = _lib("attention_diff_prefill").sb_diff_prefill(
         _ptr(q), _ptr(gate), int(gate_stride), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
         block_table.shape[1], _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len),
@@ -998,7 +1026,8 @@ def diff_attention_step(q, gate, k_store, v_store, block_table, ctx, heads, kv_h
             and (gate is None or (gate.stride(0) % 2 == 0 and gate.data_ptr() % 4 == 0))):
         return diff_attention_prefill(q, gate, k_store, v_store, block_table, ctx.seq_slot, ctx.seq_q_start,
                                       ctx.seq_q_len, ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first, heads,
-                                      kv_heads, dim, v_dim, scale, lam, out_scale, eps, window)
+                                      kv_heads, dim, v_dim, scale, lam, out_scale, eps, window,
+                                      status=ctx.status, max_q_len=ctx.max_q_len)
     if ctx.max_q_len == 1 and diff_prefill_takes(q.dtype, dim, v_dim):
         return diff_attention_decode(q, gate, k_store, v_store, block_table, ctx.seq_slot, ctx.seq_kv_len, heads,
                                      kv_heads, dim, v_dim, scale, lam, out_scale, eps, window,

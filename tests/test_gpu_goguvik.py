@@ -214,7 +214,7 @@ def test_attention_alone_with_one_key_that_stands_out(heads, groups, dim, vdim, 
 
 
 @pytest.mark.parametrize("heads, groups, dim, vdim", [(4, 2, 16, 32), (2, 2, 32, 64), (3, 1, 64, 128), (2, 1, 128, 64),
-                                                      (2, 1, 16, 128), (2, 2, 128, 128)])
+                                                      (2, 1, 16, 128), (2, 2, 128, 128), (4, 2, 64, 64)])
 def test_prompt_attention_on_tensor_cores_alone(heads, groups, dim, vdim):
     """Ragged sequences in one launch: a prompt from position 0, a portion that starts in the middle
     of a page behind 300 cached keys, a two-token portion; one key far back and one at the page
@@ -227,7 +227,7 @@ def test_prompt_attention_on_tensor_cores_alone(heads, groups, dim, vdim):
     ks, vs, table = pages.store()
     lam, lam0, eps, scale = 0.45, 0.2, 1e-6, 0.25
     # (first position, count) per sequence; all read slot 1's pages, which is fine for reading
-    spans = [(0, 150), (300, 333), (698, 2), (63, 66)]
+    spans = [(0, 150), (300, 333), (698, 2), (63, 66), (1, 128), (130, 129)]
     total = sum(n for _, n in spans)
     g = torch.Generator().manual_seed(7)
     q = torch.randn(total, heads, 2, dim, generator=g, dtype=torch.float64) * 0.3
@@ -246,17 +246,25 @@ def test_prompt_attention_on_tensor_cores_alone(heads, groups, dim, vdim):
         at += n
     tiles = [(i, f) for i, (_, n) in enumerate(spans) for f in range(0, n, 64)]
     for window in (None, 70):
-        got = ops.diff_attention_prefill(qd, gd, ks, vs, table, i32([1] * len(spans)), i32(starts),
-                                         i32([n for _, n in spans]), i32([p + n for p, n in spans]),
-                                         i32([i for i, _ in tiles]), i32([f for _, f in tiles]), heads, groups, dim,
-                                         vdim, scale, lam, 1 - lam0, eps, window)
+        step = (i32([1] * len(spans)), i32(starts), i32([n for _, n in spans]), i32([p + n for p, n in spans]),
+                i32([i for i, _ in tiles]), i32([f for _, f in tiles]))
+        got = ops.diff_attention_prefill(qd, gd, ks, vs, table, *step, heads, groups, dim, vdim, scale, lam, 1 - lam0,
+                                         eps, window, kernel="mma")
+        kernels = [("mma.sync", got)]
+        if ops.diff_prefill_tc_takes(t, dim, vdim):       # the same on the tcgen05 kernel
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            kernels.append(("tcgen05", ops.diff_attention_prefill(qd, gd, ks, vs, table, *step, heads, groups, dim, vdim,
+                                                                  scale, lam, 1 - lam0, eps, window, status=status,
+                                                                  kernel="tcgen05")))
+            assert int(status.item()) == 0, "a wait inside the tcgen05 kernel ran out"
         for (p0, n), s0 in zip(spans, starts):
             positions = torch.arange(p0, p0 + n)
             want = torch.cat([plain.plain_differential_head(
                 qs[s0:s0 + n, h, 0], qs[s0:s0 + n, h, 1], pages.k[:, h // (heads // groups), 0],
                 pages.k[:, h // (heads // groups), 1], pages.v[:, h // (heads // groups)], scale, lam, lam0, eps,
                 positions, window) for h in range(heads)], -1) * torch.sigmoid(gs[s0:s0 + n])
-            close(got[s0:s0 + n], want, "bfloat16", f"positions {p0}..{p0 + n - 1}, window {window}", bf16=2.5e-2)
+            for name, result in kernels:
+                close(result[s0:s0 + n], want, "bfloat16", f"{name}: positions {p0}..{p0 + n - 1}, window {window}", bf16=2.5e-2)
         # the other kernel on the same rows agrees
         pos = i32([p for p0, n in spans for p in range(p0, p0 + n)])
         other = ops.diff_attention(qd, gd, ks, vs, table, i32([1] * total), pos, heads, groups, dim, vdim, scale, lam,
