@@ -81,7 +81,7 @@ def main(argv=None) -> int:
 
         from .config import load_config
 
-        vocab = load_config(args.model_path).vocab_size
+        vocab = load_config(args.model_path).to_model_spec().vocab_size
         draw = torch.Generator().manual_seed(args.prompt_seed)
         prompts = [torch.randint(0, vocab, (int(n),), generator=draw).tolist()
                    for n in args.prompt_lens.split(",") if n.strip()]

@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(DP_THREADS)
 diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store, const bf16* __restrict__ v_store,
                    const int* __restrict__ block_table, int table_stride, const int* __restrict__ row_slot,
                    const int* __restrict__ row_kv_len, int heads, int kv_heads, float scale_log2, int window,
-                   int n_splits, float* __restrict__ part) {
+                   int n_splits, float* __restrict__ part, int early) {
   constexpr int CQ = QK / 8, CV = VD / 8;
   constexpr int K_BYTES = SB_PAGE_TOKENS * QK * 2, V_BYTES = SB_PAGE_TOKENS * VD * 2;
   constexpr int KSTEPS = QK / 32, NBLK = VD / 8, PER = VD + 2;
@@ -303,12 +303,16 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
   float* meet = reinterpret_cast<float*>(k_tiles);   // after the walk: [4 warps][2 maps][16 rows][PER]
 
   pdl_trigger();
-  pdl_wait();
-  SB_BEHIND_WAIT(q);
-  SB_BEHIND_WAIT(k_store);
-  SB_BEHIND_WAIT(v_store);
-  SB_BEHIND_WAIT(row_slot);
-  SB_BEHIND_WAIT(row_kv_len);
+  // `early`: the caller vouches that the rows' lengths, the page table and every cached key and value
+  // but the newest token's were complete before this step's first kernel started, and that nothing
+  // else in this step writes them.  Then the first pages (all but a row's last one, which holds the
+  // token this step has just filed) are asked for before the dependent-launch wait, while the kernels
+  // before this one still run.
+  if (!early) {
+    pdl_wait();
+    SB_BEHIND_WAIT(row_slot);
+    SB_BEHIND_WAIT(row_kv_len);
+  }
   const int group = heads / kv_heads, chunks = (group + 15) / 16;
   const int split = blockIdx.x, kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks, row = blockIdx.z;
   const int head0 = kvh * group + chunk * 16, n_heads = min(16, group - chunk * 16);
@@ -322,6 +326,7 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
   const int n_pages = p_end - p_begin;
   float* mine = part + (((size_t)row * heads + head0) * n_splits + split) * 2 * PER;   // + r * n_splits * 2 * PER per head
   if (n_pages <= 0) {      // more parts than pages: this part is empty
+    if (early) pdl_wait();
     for (int i = tid; i < n_heads * 2; i += DP_THREADS) {
       float* dst = mine + (size_t)(i >> 1) * n_splits * 2 * PER + (i & 1) * PER;
       dst[0] = -INFINITY;
@@ -330,13 +335,6 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
     return;
   }
   const int* pages = block_table + (size_t)row_slot[row] * table_stride;
-  {
-    const bf16* src = q + (size_t)row * heads * QK;
-    for (int idx = tid; idx < 16 * CQ; idx += DP_THREADS) {
-      const int r = idx / CQ, c = idx % CQ;
-      cp_async16(q_tile + tile_offset<QK>(r, c), src + (size_t)(head0 + min(r, n_heads - 1)) * QK + c * 8);
-    }
-  }
   auto load_kv = [&](int t, int buf) {
     const int page = pages[p_begin + t];
     const bf16* ks = k_store + page_row(page, kvh, 0, kv_heads, QK);
@@ -346,11 +344,29 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
     for (int idx = tid; idx < SB_PAGE_TOKENS * CV; idx += DP_THREADS)
       cp_async16(v_tiles + buf * V_BYTES + tile_offset<VD>(idx / CV, idx % CV), vs + (size_t)idx * 8);
   };
+  // before the wait: the pages of the first stages that earlier steps filled
+  bool asked[DD_STAGES - 1];
 #pragma unroll
   for (int s = 0; s < DD_STAGES - 1; ++s) {
-    if (s < n_pages) load_kv(s, s);
-    cp_commit();
+    asked[s] = early && s < n_pages && p_begin + s < page_hi;
+    if (asked[s]) load_kv(s, s);
   }
+  if (early) pdl_wait();
+  SB_BEHIND_WAIT(q);
+  SB_BEHIND_WAIT(k_store);
+  SB_BEHIND_WAIT(v_store);
+  {
+    const bf16* src = q + (size_t)row * heads * QK;
+    for (int idx = tid; idx < 16 * CQ; idx += DP_THREADS) {
+      const int r = idx / CQ, c = idx % CQ;
+      cp_async16(q_tile + tile_offset<QK>(r, c), src + (size_t)(head0 + min(r, n_heads - 1)) * QK + c * 8);
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < DD_STAGES - 1; ++s)
+    if (!asked[s] && s < n_pages) load_kv(s, s);
+  cp_commit();                       // one group: the queries and the first stages
+  cp_wait<0>();
 
   float o[2][NBLK][4];
 #pragma unroll
@@ -361,6 +377,8 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
   const int q_row = (lane & 7) + ((lane >> 3) & 1) * 8;
 
   for (int t = 0; t < n_pages; ++t) {
+    // the first DD_STAGES - 1 pages came in one group, awaited above; page t >= DD_STAGES - 1 is the group
+    // committed DD_STAGES - 1 iterations ago, so all but the newest DD_STAGES - 2 groups must be done
     cp_wait<DD_STAGES - 2>();
     __syncthreads();                 // page t has landed for everyone, and everyone is done with page t - 1
     if (t + DD_STAGES - 1 < n_pages) load_kv(t + DD_STAGES - 1, (t + DD_STAGES - 1) % DD_STAGES);
@@ -532,7 +550,7 @@ __global__ void diff_decode_merge_kernel(const float* __restrict__ part, const b
 template <int QK, int VD>
 static int launch_decode(const void* q, const void* k_store, const void* v_store, const int* block_table,
                          int table_stride, const int* row_slot, const int* row_kv_len, int rows, int heads,
-                         int kv_heads, float scale, int window, int n_splits, float* part, cudaStream_t s) {
+                         int kv_heads, float scale, int window, int n_splits, float* part, int early, cudaStream_t s) {
   constexpr int ring = DD_STAGES * SB_PAGE_TOKENS * (QK + VD) * 2, meeting = 4 * 2 * 16 * (VD + 2) * 4;
   const int smem = 16 * QK * 2 + (ring > meeting ? ring : meeting);     // the meeting area lies over the ring
   static bool configured = false;
@@ -544,7 +562,7 @@ static int launch_decode(const void* q, const void* k_store, const void* v_store
   const int chunks = (heads / kv_heads + 15) / 16;
   return launch_dependent(diff_decode_kernel<QK, VD>, dim3(n_splits, kv_heads * chunks, rows), dim3(DP_THREADS), smem, s,
       (const bf16*)q, (const bf16*)k_store, (const bf16*)v_store, block_table, table_stride, row_slot, row_kv_len,
-      heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part);
+      heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part, early);
 }
 
 template <int QK, int VD>
@@ -607,17 +625,17 @@ int sb_diff_prefill(const void* q, const void* gate, int gate_stride, void* out,
 
 // One query row per sequence (its newest token, already in the cache): q [rows, heads * 2 * dim], out
 // [rows, heads * v_dim]; row_kv_len[r] counts the row's own key.  part: float scratch of
-// rows * heads * n_splits * 2 * (v_dim + 2).  Two launches (the walk, the merge).  v_dim <= 256.
+// rows * heads * n_splits * 2 * (v_dim + 2).  Two launches (the walk, the merge).  early: see the kernel.
 int sb_diff_decode(const void* q, const void* gate, int gate_stride, void* out, const void* k_store,
                    const void* v_store, const int* block_table, int table_stride, const int* row_slot,
                    const int* row_kv_len, int rows, int heads, int kv_heads, int dim, int v_dim, float scale,
-                   int window, float lambda, float out_scale, float eps, int n_splits, float* part,
+                   int window, float lambda, float out_scale, float eps, int n_splits, float* part, int early,
                    cudaStream_t s) {
   if (rows == 0) return 0;
   if (kv_heads <= 0 || heads % kv_heads || !sb_diff_prefill_takes(dim, v_dim) || n_splits < 1 || n_splits > 65535) return -2;
   int rc = -2;
 #define ARGS q, k_store, v_store, block_table, table_stride, row_slot, row_kv_len, rows, heads, kv_heads, scale, window, \
-             n_splits, part, s
+             n_splits, part, early, s
 #define BY_V(QK) switch (v_dim) { case 32: rc = launch_decode<QK, 32>(ARGS); break; case 64: rc = launch_decode<QK, 64>(ARGS); break; \
                                   case 128: rc = launch_decode<QK, 128>(ARGS); break; default: return -2; } break;
   switch (dim) {

@@ -987,12 +987,17 @@ def diff_attention(q, gate, k_store, v_store, block_table, tok_slot, tok_pos, he
 
 
 def diff_attention_decode(q, gate, k_store, v_store, block_table, row_slot, row_kv_len, heads, kv_heads, dim, v_dim,
-                          scale, lam, out_scale, eps, window=None, n_splits=None, kv_hint=0):
+                          scale, lam, out_scale, eps, window=None, n_splits=None, kv_hint=0, early=False):
     """``diff_attention`` for one new token per sequence, on tensor cores (bfloat16): the query heads
     of a key/value head are the MMA's rows, so a page is read once for all of them and both maps;
     each row's keys are cut into ``n_splits`` parts (chosen from ``kv_hint``, the longest sequence,
     so that the blocks fill the GPU) that a second kernel joins.  Row ``i`` is the newest token of the
-    sequence in ``row_slot[i]``, already in the cache; ``row_kv_len[i]`` counts it."""
+    sequence in ``row_slot[i]``, already in the cache; ``row_kv_len[i]`` counts it.
+
+    ``early``: the caller vouches that ``row_kv_len``, the page table and every cached key and value
+    but the newest token's were complete before this step's first kernel started (``embedding(...,
+    fence=True)``) and that nothing else in this step writes them; the kernel then asks for its first
+    pages before its dependent-launch wait, while the kernels before it still run."""
     gate_stride = _diff_check(q, gate, k_store, v_store, heads, kv_heads, dim, v_dim)
     if not diff_prefill_takes(q.dtype, dim, v_dim):
         raise KernelError(f"the tensor-core differential attention is not built for dim {dim}, v_dim {v_dim} in {q.dtype}")
@@ -1003,14 +1008,16 @@ def diff_attention_decode(q, gate, k_store, v_store, block_table, row_slot, row_
     if n_splits is None:
         blocks = rows * kv_heads * (-(-(heads // kv_heads) // 16))
         pages = max(1, -(-kv_hint // PAGE_TOKENS))
-        n_splits = max(1, min(pages, (2 * 148) // max(blocks, 1), 64))
+        # measured at 2,048 keys: a part wants seven pages or more (shorter parts pay the ring's start
+        # and the merge for too little streaming), and all blocks resident at once (two fit on an SM)
+        n_splits = max(1, min(pages // 7, (2 * 148) // max(blocks, 1), 64))
     out = torch.empty((rows, heads * v_dim), dtype=q.dtype, device=q.device)
     part = torch.empty((rows * heads * n_splits * 2 * (v_dim + 2),), dtype=torch.float32, device=q.device)
     rc = _lib("attention_diff_prefill").sb_diff_decode(
         _ptr(q), _ptr(gate), int(gate_stride), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
         block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, dim, v_dim,
         ctypes.c_float(scale), int(window or 0), ctypes.c_float(lam), ctypes.c_float(out_scale), ctypes.c_float(eps),
-        int(n_splits), _ptr(part), _stream())
+        int(n_splits), _ptr(part), int(bool(early) and EARLY_READS), _stream())
     _check(rc, "diff_attention_decode", 2)
     return out
 
@@ -1031,7 +1038,7 @@ def diff_attention_step(q, gate, k_store, v_store, block_table, ctx, heads, kv_h
     if ctx.max_q_len == 1 and diff_prefill_takes(q.dtype, dim, v_dim):
         return diff_attention_decode(q, gate, k_store, v_store, block_table, ctx.seq_slot, ctx.seq_kv_len, heads,
                                      kv_heads, dim, v_dim, scale, lam, out_scale, eps, window,
-                                     kv_hint=ctx.max_kv_len)
+                                     kv_hint=ctx.max_kv_len, early=ctx.fenced)
     return diff_attention(q, gate, k_store, v_store, block_table, ctx.tok_slot, ctx.tok_pos, heads, kv_heads,
                           dim, v_dim, scale, lam, out_scale, eps, window, kv_hint=ctx.max_kv_len)
 

@@ -504,3 +504,56 @@ def test_random_weights_from_the_library_run_in_bfloat16(tmp_path_factory):
     out = engine.complete([[1, 2, 3], [4]], 12, temperature=0.8, seed=3)
     assert [len(c.tokens) for c in out] == [12, 12]
     assert all(0 <= t < 200 for c in out for t in c.tokens)
+
+
+# ------------------------------------------------------------------------------ the programs
+
+def test_command_line_and_trace_replay(tmp_path_factory, tmp_path):
+    """``python -m starter_b200 generate`` and ``bin/trace_run`` pick the design by its config.json."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder, cfg, w = case(tmp_path_factory, "GD")
+    prompts = [random_prompt(5, cfg["vocab"], 1), random_prompt(19, cfg["vocab"], 2)]
+    text = ";".join(",".join(str(t) for t in p) for p in prompts)
+    out = subprocess.run([sys.executable, "-m", "starter_b200", "generate", "--model-path", folder, "--input-ids", text,
+                          "--max-new-tokens", "6", "--dtype", "float32"], cwd=root, capture_output=True, text=True,
+                         timeout=600)
+    assert out.returncode == 0, out.stderr
+    lines = [json.loads(line) for line in out.stdout.splitlines() if line.startswith("{")]
+    assert [line["tokens"] for line in lines] == [plain.plain_generate(cfg, w, p, 6) for p in prompts]
+    out = subprocess.run([sys.executable, "-m", "starter_b200", "generate", "--model-path", folder, "--prompt-lens", "4,2",
+                          "--max-new-tokens", "3"], cwd=root, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+
+    # a trace: two unequal requests start together, are decoded together, the shorter one ends first
+    a, b = random_prompt(140, cfg["vocab"], 5), random_prompt(70, cfg["vocab"], 6)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:130], "want": [0, 129]},
+                                     {"id": "b", "tokens": b[:66], "want": [65]}], "end": []}]
+    for i in range(10):
+        entries = [{"id": "a", "tokens": [a[130 + i]], "want": [0]}]
+        if i < 4:
+            entries.append({"id": "b", "tokens": [b[66 + i]], "want": [0] if i % 2 else []})
+        steps.append({"step": 1 + i, "entries": entries, "end": (["b"] if i == 3 else []) + (["a"] if i == 9 else [])})
+    for dtype in DTYPES:
+        out_dir = str(tmp_path / dtype)
+        proc = subprocess.Popen([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                                 "--out", out_dir, "--max-tokens", "256"], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
+                                text=True)
+        for record in steps:
+            proc.stdin.write(json.dumps(record) + "\n")
+            proc.stdin.flush()
+            assert proc.stdout.readline().strip() == f"done {record['step']}"
+        proc.stdin.close()
+        assert proc.wait(timeout=120) == 0
+        want_a, want_b = plain.plain_forward(cfg, w, a), plain.plain_forward(cfg, w, b)
+        read = lambda s: torch.from_numpy(np.fromfile(os.path.join(out_dir, f"{s}.f32"), dtype="<f4").reshape(-1, cfg["vocab"]))  # noqa: E731
+        assert_close(read(0), torch.stack([want_a[0], want_a[129], want_b[65]]), dtype, "the first step")
+        for i in range(10):
+            rows = [want_a[130 + i]] + ([want_b[66 + i]] if i < 4 and i % 2 else [])
+            assert_close(read(1 + i), torch.stack(rows), dtype, f"step {1 + i}")
