@@ -11,7 +11,8 @@ runs exactly those tokens through the library's own model, step function, cache 
 ones generation uses), writes ``OUT/<step>.f32`` (little-endian float32 ``[wanted, vocab]``, in the
 order of the entries and of ``want``) when something is wanted, releases what the requests in ``end``
 hold, and prints ``done <step>``.  It samples nothing.  ``--max-tokens`` sizes the cache: the most
-tokens live requests hold at any time, each request rounded up to 64 (the cache's page).
+tokens live requests hold at any time, not counting what a request's last page (64 tokens) leaves
+unused; the cache gets one page more for every request that can be live at once (up to 256).
 
 The reference has no such program; its nearest idea is the platform's teacher-forced replay of the
 emitted tokens (QWEN_ENGINE_CONTRACT.md:105-123).
@@ -41,7 +42,9 @@ def main(argv=None) -> int:
 
     os.makedirs(args.out, exist_ok=True)
     model = load_model(args.model, args.dtype)
-    pages = max(pages_for(args.max_tokens), 1)
+    # every live request may leave part of its last page unused: a page of slack for each
+    live = max(1, min(args.max_tokens, 256))
+    pages = max(pages_for(args.max_tokens), 1) + live
     runner = ModelRunner(model, pages * PAGE_TOKENS, max_sequences=min(pages, 4096), use_graphs=False)
     print(f"[trace_run] model loaded; cache of {pages} pages of {PAGE_TOKENS} tokens", file=sys.stderr,
           flush=True)

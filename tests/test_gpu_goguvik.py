@@ -543,7 +543,7 @@ def test_command_line_and_trace_replay(tmp_path_factory, tmp_path):
     for dtype in DTYPES:
         out_dir = str(tmp_path / dtype)
         proc = subprocess.Popen([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
-                                 "--out", out_dir, "--max-tokens", "256"], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
+                                 "--out", out_dir, "--max-tokens", "210"], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
                                 text=True)
         for record in steps:
             proc.stdin.write(json.dumps(record) + "\n")
