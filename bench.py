@@ -285,13 +285,14 @@ DESIGN_SIZES = {
 
 
 def goguvik_config(size: dict, layers: int) -> dict:
-    """Goguvik at ``size``: four streams, every second layer on the keys and values of the layer before."""
+    """Goguvik at ``size``: four streams; of every three layers the second and third attend over the
+    keys and values of the first."""
     out = []
     for i in range(layers):
-        mixer = dict(heads=size["heads"], kv_heads=size["kv_heads"], dim=64, vdim=128, scale=0.125, diff=0.3,
-                     q_temp=dict(coef=0.3, every=64))
-        if i % 2:
-            mixer["kv_from"] = i - 1
+        mixer = dict(heads=size["heads"], kv_heads=size["kv_heads"], dim=64, vdim=128, scale=0.125, diff=0.25,
+                     q_temp=dict(coef=0.5, every=128))
+        if i % 3:
+            mixer["kv_from"] = i - i % 3
         out.append(dict(type="attention", mixer=mixer, mlp=dict(kind="dense", ff=size["ff"])))
     return dict(architecture="Goguvik", vocab=size["vocab"], width=size["width"], streams=4,
                 norm=dict(eps=1e-6), layers=out)
@@ -381,7 +382,7 @@ def design_compare(args) -> int:
                 def prepare(b, e):
                     k, v = cache.entry_pages(e)
                     return ops.diff_prepare(proj, b.mixer.bias, heads, kvh, sp.head_dim, sp.value_dim, m.gate_size,
-                                            (0.3, 64), ctx.tok_pos, ctx.tok_slot, cache.block_table, k, v)
+                                            (0.5, 128), ctx.tok_pos, ctx.tok_slot, cache.block_table, k, v)
 
                 def attend(b, e):
                     k, v = cache.entry_pages(e)

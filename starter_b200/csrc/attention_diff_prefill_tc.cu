@@ -583,7 +583,7 @@ extern "C" {
 // 1 if the kernel is built for these sizes.
 int sb_diff_prefill_tc_takes(int dim, int v_dim) { return dim == 64 && (v_dim == 64 || v_dim == 128); }
 
-// The contract of sb_diff_prefill (work list in tiles of 64 queries); n_tokens rows in q/out, n_pages
+// Arguments as sb_diff_prefill takes them (work list in tiles of 64 queries); n_tokens rows in q/out, n_pages
 // pages in the stores.  The gate's rows must start on 16-byte boundaries.  Returns -2 for sizes it is
 // not built for.
 int sb_diff_prefill_tc(const void* q, const void* gate, int gate_stride, void* out, const void* k_store,

@@ -28,8 +28,8 @@ def test_every_size_and_constant_comes_from_the_config():
     assert (spec.vocab_size, spec.hidden_size, spec.streams, len(spec.layers)) == (300, 80, 2, 3)
     first, middle, last = (layer.mixer for layer in spec.layers)
     assert (first.num_heads, first.num_kv_heads, first.head_dim, first.value_dim) == (6, 1, 24, 16)
-    assert (first.scale, first.lambda_init, first.norm_eps) == (0.15, 0.3, 1e-6)
-    assert (first.q_temperature.coef, first.q_temperature.every) == (0.3, 64)
+    assert (first.scale, first.lambda_init, first.norm_eps) == (0.15, 0.28, 1e-6)
+    assert (first.q_temperature.coef, first.q_temperature.every) == (0.35, 48)
     assert middle.q_temperature is None and (middle.num_heads, middle.head_dim, middle.value_dim) == (2, 32, 32)
     assert first.own_kv and middle.own_kv and not last.own_kv
     assert spec.layers[2].feed_forward.intermediate_size == 64

@@ -397,7 +397,7 @@ def test_every_layer_against_the_plain_layers(tmp_path_factory, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", CONFIGS)
 def test_prompt_then_tokens_one_by_one(tmp_path_factory, name, dtype):
-    """The temperature's steps (every 8, 5 or 64 positions) and a page border are crossed while decoding."""
+    """The temperature's steps (every 8, 5, 48 or 16 positions) and a page border are crossed while decoding."""
     from starter_b200.engine import StepEntry
 
     _, cfg, w = case(tmp_path_factory, name)

@@ -37,9 +37,9 @@ G_B = dict(architecture="Goguvik", vocab=131, width=96, streams=1, norm=dict(eps
 # two streams; one key/value head for six query heads; key rows of 48; layers that differ in their
 # head counts; no temperature in the middle layer; a shared layer whose source is two layers back
 G_C = dict(architecture="Goguvik", vocab=300, width=80, streams=2, norm=dict(eps=1e-6), layers=[
-    _layer(_mixer(6, 1, 24, 16, 0.15, 0.3, (0.3, 64)), 112),
+    _layer(_mixer(6, 1, 24, 16, 0.15, 0.28, (0.35, 48)), 112),
     _layer(_mixer(2, 2, 32, 32, 0.125, 0.2), 112),
-    _layer(_mixer(6, 1, 24, 16, 0.15, 0.3, (0.3, 64), kv_from=0), 64),
+    _layer(_mixer(6, 1, 24, 16, 0.15, 0.28, (0.35, 48), kv_from=0), 64),
 ])
 
 # sizes the tensor-core prompt kernel takes (key rows of 32 and 64, value rows of 32 and 64), so that
