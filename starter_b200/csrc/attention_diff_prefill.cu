@@ -40,6 +40,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Distributed shared memory: the address of `addr` (shared window) in block `rank` of the cluster, a load
+// from there, and the two cluster barriers (one that publishes this block's writes, one that does not).
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(addr), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ float cluster_load(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_rendezvous() {
+  asm volatile("barrier.cluster.arrive.relaxed;\n\tbarrier.cluster.wait;" ::: "memory");
+}
+
 // Byte offset of 16-byte column `chunk` of `row` in a [rows][D] bfloat16 tile with swizzled columns.
 template <int D> __device__ __forceinline__ int tile_offset(int row, int chunk) {
   constexpr int C = D / 8;
@@ -285,22 +304,121 @@ diff_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate, i
 // accumulators per map, the warps' results meet in shared memory, and the block leaves its part as
 // (maximum, sum, accumulator) per head and map in scratch memory.  diff_decode_merge joins the parts
 // and finishes the head (difference, unit norm, gate).
+//
+// CLUSTER: the parts of a (row, key/value head) are the blocks of one thread-block cluster (n_splits
+// <= 8).  Each leaves its part in its own shared memory; after a cluster barrier block s joins and
+// finishes the heads s, s + n_splits, ... (a warp a head, reading every block's part through
+// distributed shared memory), so there is neither scratch memory nor a second launch.
 #define DD_STAGES 3
+#define DD_CLUSTER_MAX 8
 
-template <int QK, int VD>
+// own: this block's part, [16 heads][2 maps][VD + 2] floats (maximum, sum, accumulator) in shared memory
+// at the same address in every block of the cluster.
+template <int VD>
+__device__ __forceinline__ void diff_decode_cluster_finish(const float* own, int split, int n_splits, int n_heads,
+                                                           int row, int heads, int head0, const bf16* gate,
+                                                           int gate_stride, bf16* out, const DiffPrefillTail& tail) {
+  constexpr int PER = VD + 2, CPL = VD / 32;      // CPL columns a lane: lane, lane + 32, ...
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the gate's values are asked for ahead of the barrier and of the remote loads (of a head's, a pass ahead)
+  float g[CPL];
+  auto ask_gate = [&](int r) {
+#pragma unroll
+    for (int i = 0; i < CPL; ++i)
+      g[i] = gate && r < n_heads ? __bfloat162float(gate[(size_t)row * gate_stride + (size_t)(head0 + r) * VD + lane + 32 * i]) : 0.f;
+  };
+  ask_gate(split + n_splits * warp);
+  cluster_sync();                                  // every block's part is written and visible
+  const uint32_t base = smem_u32(own);
+  for (int r = split + n_splits * warp; r < n_heads; r += n_splits * (DP_THREADS / 32)) {
+    float gv[CPL];
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) gv[i] = g[i];
+    ask_gate(r + n_splits * (DP_THREADS / 32));
+    // every part's values first (the remote loads are in flight together), then the arithmetic; an empty
+    // part holds (-inf, 0, zeros) and gets the weight 0
+    float m[2][DD_CLUSTER_MAX], l[2][DD_CLUSTER_MAX], av[2][DD_CLUSTER_MAX][CPL];
+#pragma unroll
+    for (int sp = 0; sp < DD_CLUSTER_MAX; ++sp) {
+      if (sp < n_splits) {
+#pragma unroll
+        for (int mp = 0; mp < 2; ++mp) {
+          const uint32_t at = cluster_addr(base + (uint32_t)((r * 2 + mp) * PER) * 4u, sp);
+          m[mp][sp] = cluster_load(at);
+          l[mp][sp] = cluster_load(at + 4u);
+#pragma unroll
+          for (int i = 0; i < CPL; ++i) av[mp][sp][i] = cluster_load(at + (uint32_t)(2 + lane + 32 * i) * 4u);
+        }
+      }
+    }
+    float big[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int sp = 0; sp < DD_CLUSTER_MAX; ++sp)
+      if (sp < n_splits) { big[0] = fmaxf(big[0], m[0][sp]); big[1] = fmaxf(big[1], m[1][sp]); }
+    float den[2] = {0.f, 0.f}, a[2][CPL];
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) a[0][i] = a[1][i] = 0.f;
+#pragma unroll
+    for (int sp = 0; sp < DD_CLUSTER_MAX; ++sp) {
+      if (sp < n_splits) {
+#pragma unroll
+        for (int mp = 0; mp < 2; ++mp) {
+          const float w = m[mp][sp] == -INFINITY ? 0.f : exp2f(m[mp][sp] - big[mp]);
+          den[mp] += l[mp][sp] * w;
+#pragma unroll
+          for (int i = 0; i < CPL; ++i) a[mp][i] += av[mp][sp][i] * w;
+        }
+      }
+    }
+    float d[CPL], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+      d[i] = a[0][i] / den[0] - tail.lambda * (a[1][i] / den[1]);
+      ss += d[i] * d[i];
+    }
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sh);
+    const float norm = rsqrtf(ss / (float)VD + tail.eps) * tail.out_scale;
+    const int head = head0 + r;
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+      const int c = lane + 32 * i;
+      float v = d[i] * norm;
+      if (gate) v *= 1.f / (1.f + __expf(-gv[i]));
+      out[((size_t)row * heads + head) * VD + c] = __float2bfloat16_rn(v);
+    }
+  }
+  cluster_rendezvous();                            // nobody leaves while its shared memory is still read
+}
+
+template <int QK, int VD, bool CLUSTER>
 __global__ void __launch_bounds__(DP_THREADS)
 diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store, const bf16* __restrict__ v_store,
                    const int* __restrict__ block_table, int table_stride, const int* __restrict__ row_slot,
                    const int* __restrict__ row_kv_len, int heads, int kv_heads, float scale_log2, int window,
-                   int n_splits, float* __restrict__ part, int early) {
+                   int n_splits, float* __restrict__ part, int early, const bf16* __restrict__ gate,
+                   int gate_stride, bf16* __restrict__ out, DiffPrefillTail tail) {
   constexpr int CQ = QK / 8, CV = VD / 8;
   constexpr int K_BYTES = SB_PAGE_TOKENS * QK * 2, V_BYTES = SB_PAGE_TOKENS * VD * 2;
   constexpr int KSTEPS = QK / 32, NBLK = VD / 8, PER = VD + 2;
+  // a warp's rows in the meeting area lie VD + 8 floats apart: a quad writes 8 consecutive floats and the rows
+  // of a half warp are 8 banks apart, so its 8-byte stores meet no bank twice
+  constexpr int MPER = VD + 8;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* q_tile = smem;                            // [16][QK]
   uint8_t* k_tiles = smem + 16 * QK * 2;             // DD_STAGES x [64][QK]
   uint8_t* v_tiles = k_tiles + DD_STAGES * K_BYTES;  // DD_STAGES x [64][VD]
-  float* meet = reinterpret_cast<float*>(k_tiles);   // after the walk: [4 warps][2 maps][16 rows][PER]
+  float* meet = reinterpret_cast<float*>(k_tiles);   // after the walk: [4 warps][2 maps][16 rows][MPER]
+  float* own = meet + 4 * 2 * 16 * MPER;             // CLUSTER: this block's part, [16 rows][2 maps][PER]
+  // -DDD_TIMELINE (a build of its own, for measuring; the library never makes it): thread 0 of every block
+  // leaves the global timer at the ends of its phases, and its SM, in `part`.
+#ifdef DD_TIMELINE
+  unsigned long long tl[8];
+#define TL(k) do { asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tl[k])); } while (0)
+  TL(0);
+#else
+#define TL(k)
+#endif
 
   pdl_trigger();
   // `early`: the caller vouches that the rows' lengths, the page table and every cached key and value
@@ -327,6 +445,12 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
   float* mine = part + (((size_t)row * heads + head0) * n_splits + split) * 2 * PER;   // + r * n_splits * 2 * PER per head
   if (n_pages <= 0) {      // more parts than pages: this part is empty
     if (early) pdl_wait();
+    if (CLUSTER) {
+      SB_BEHIND_WAIT(gate);
+      for (int i = tid; i < 16 * 2 * PER; i += DP_THREADS) own[i] = i % PER == 0 ? -INFINITY : 0.f;
+      diff_decode_cluster_finish<VD>(own, split, n_splits, n_heads, row, heads, head0, gate, gate_stride, out, tail);
+      return;
+    }
     for (int i = tid; i < n_heads * 2; i += DP_THREADS) {
       float* dst = mine + (size_t)(i >> 1) * n_splits * 2 * PER + (i & 1) * PER;
       dst[0] = -INFINITY;
@@ -335,8 +459,13 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
     return;
   }
   const int* pages = block_table + (size_t)row_slot[row] * table_stride;
-  auto load_kv = [&](int t, int buf) {
-    const int page = pages[p_begin + t];
+  // A page's number is asked for a whole iteration before its copies are issued: the lookup's latency
+  // (the table lies in L2 at best) would otherwise sit in front of every iteration's prefetch.
+  int first_pages[DD_STAGES];
+#pragma unroll
+  for (int st = 0; st < DD_STAGES; ++st) first_pages[st] = st < n_pages ? pages[p_begin + st] : 0;
+  int page_next = first_pages[DD_STAGES - 1];
+  auto load_kv = [&](int page, int buf) {
     const bf16* ks = k_store + page_row(page, kvh, 0, kv_heads, QK);
     const bf16* vs = v_store + page_row(page, kvh, 0, kv_heads, VD);
     for (int idx = tid; idx < SB_PAGE_TOKENS * CQ; idx += DP_THREADS)
@@ -349,9 +478,11 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
 #pragma unroll
   for (int s = 0; s < DD_STAGES - 1; ++s) {
     asked[s] = early && s < n_pages && p_begin + s < page_hi;
-    if (asked[s]) load_kv(s, s);
+    if (asked[s]) load_kv(first_pages[s], s);
   }
+  TL(1);
   if (early) pdl_wait();
+  TL(2);
   SB_BEHIND_WAIT(q);
   SB_BEHIND_WAIT(k_store);
   SB_BEHIND_WAIT(v_store);
@@ -364,9 +495,10 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
   }
 #pragma unroll
   for (int s = 0; s < DD_STAGES - 1; ++s)
-    if (!asked[s] && s < n_pages) load_kv(s, s);
+    if (!asked[s] && s < n_pages) load_kv(first_pages[s], s);
   cp_commit();                       // one group: the queries and the first stages
   cp_wait<0>();
+  TL(3);
 
   float o[2][NBLK][4];
 #pragma unroll
@@ -381,8 +513,9 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
     // committed DD_STAGES - 1 iterations ago, so all but the newest DD_STAGES - 2 groups must be done
     cp_wait<DD_STAGES - 2>();
     __syncthreads();                 // page t has landed for everyone, and everyone is done with page t - 1
-    if (t + DD_STAGES - 1 < n_pages) load_kv(t + DD_STAGES - 1, (t + DD_STAGES - 1) % DD_STAGES);
+    if (t + DD_STAGES - 1 < n_pages) load_kv(page_next, (t + DD_STAGES - 1) % DD_STAGES);
     cp_commit();
+    if (t + DD_STAGES < n_pages) page_next = pages[p_begin + t + DD_STAGES];
     const int buf = t % DD_STAGES;
     const uint8_t* kt = k_tiles + buf * K_BYTES;
     const uint8_t* vt = v_tiles + buf * V_BYTES;
@@ -459,6 +592,7 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
     }
   }
   cp_wait<0>();
+  TL(4);
   __syncthreads();        // the ring is free: the warps' results meet in it
 
 #pragma unroll
@@ -469,13 +603,13 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
       l += __shfl_xor_sync(0xffffffffu, l, 1);
       l += __shfl_xor_sync(0xffffffffu, l, 2);
       const int r = (lane >> 2) + 8 * h;
-      float* dst = meet + (((size_t)warp * 2 + mp) * 16 + r) * PER;
+      float* dst = meet + ((warp * 2 + mp) * 16 + r) * MPER;
+      if (r >= n_heads) continue;        // a row past the heads of this chunk: nobody reads it
       if ((lane & 3) == 0) { dst[0] = m_run[mp][h]; dst[1] = l; }
 #pragma unroll
       for (int n = 0; n < NBLK; ++n) {
         const int col = n * 8 + (lane & 3) * 2;
-        dst[2 + col] = o[mp][n][2 * h];
-        dst[2 + col + 1] = o[mp][n][2 * h + 1];
+        *reinterpret_cast<float2*>(dst + 2 + col) = make_float2(o[mp][n][2 * h], o[mp][n][2 * h + 1]);
       }
     }
   }
@@ -484,7 +618,7 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
     const int r = item / (2 * PER), rest = item % (2 * PER), mp = rest / PER, c = rest % PER;
     float big = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) big = fmaxf(big, meet[(((size_t)w * 2 + mp) * 16 + r) * PER]);
+    for (int w = 0; w < 4; ++w) big = fmaxf(big, meet[((w * 2 + mp) * 16 + r) * MPER]);
     float value;
     if (c == 0) {
       value = big;
@@ -492,13 +626,30 @@ diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_store,
       value = 0.f;
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        const float* src = meet + (((size_t)w * 2 + mp) * 16 + r) * PER;
+        const float* src = meet + ((w * 2 + mp) * 16 + r) * MPER;
         const float f = src[0] == -INFINITY ? 0.f : exp2f(src[0] - big);
         value += src[c] * f;
       }
     }
-    mine[(size_t)r * n_splits * 2 * PER + mp * PER + c] = value;
+    if (CLUSTER) own[(r * 2 + mp) * PER + c] = value;
+    else mine[(size_t)r * n_splits * 2 * PER + mp * PER + c] = value;
   }
+  TL(5);
+  if (CLUSTER) {
+    SB_BEHIND_WAIT(gate);
+    diff_decode_cluster_finish<VD>(own, split, n_splits, n_heads, row, heads, head0, gate, gate_stride, out, tail);
+  }
+  TL(6);
+#ifdef DD_TIMELINE
+  if (tid == 0 && part) {
+    unsigned long long* dst = reinterpret_cast<unsigned long long*>(part) +
+        ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8;
+    for (int k = 0; k < 7; ++k) dst[k] = tl[k];
+    unsigned int sm;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    dst[7] = sm;
+  }
+#endif
 }
 
 // Joins the parts of one (row, head) and finishes the head.  part: [rows][heads][n_splits][2][v_dim + 2]
@@ -547,22 +698,37 @@ __global__ void diff_decode_merge_kernel(const float* __restrict__ part, const b
   }
 }
 
+// *finished: the one launch also finished the heads (the parts are a cluster); otherwise the parts are
+// in `part` and the merge kernel must follow.
 template <int QK, int VD>
 static int launch_decode(const void* q, const void* k_store, const void* v_store, const int* block_table,
                          int table_stride, const int* row_slot, const int* row_kv_len, int rows, int heads,
-                         int kv_heads, float scale, int window, int n_splits, float* part, int early, cudaStream_t s) {
-  constexpr int ring = DD_STAGES * SB_PAGE_TOKENS * (QK + VD) * 2, meeting = 4 * 2 * 16 * (VD + 2) * 4;
+                         int kv_heads, float scale, int window, int n_splits, float* part, int early,
+                         const void* gate, int gate_stride, void* out, DiffPrefillTail tail, int cluster,
+                         bool* finished, cudaStream_t s) {
+  constexpr int ring = DD_STAGES * SB_PAGE_TOKENS * (QK + VD) * 2;
+  constexpr int meeting = 4 * 2 * 16 * (VD + 8) * 4 + 16 * 2 * (VD + 2) * 4;   // the warps' results, the block's part
   const int smem = 16 * QK * 2 + (ring > meeting ? ring : meeting);     // the meeting area lies over the ring
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(diff_decode_kernel<QK, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(diff_decode_kernel<QK, VD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(diff_decode_kernel<QK, VD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int chunks = (heads / kv_heads + 15) / 16;
-  return launch_dependent(diff_decode_kernel<QK, VD>, dim3(n_splits, kv_heads * chunks, rows), dim3(DP_THREADS), smem, s,
+  const dim3 grid(n_splits, kv_heads * chunks, rows);
+  *finished = cluster && n_splits <= DD_CLUSTER_MAX;
+  if (*finished)
+    return launch_dependent_cluster(diff_decode_kernel<QK, VD, true>, grid, dim3(DP_THREADS), smem, s,
+        dim3(n_splits, 1, 1), (const bf16*)q, (const bf16*)k_store, (const bf16*)v_store, block_table, table_stride,
+        row_slot, row_kv_len, heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part, early,
+        (const bf16*)gate, gate_stride, (bf16*)out, tail);
+  return launch_dependent(diff_decode_kernel<QK, VD, false>, grid, dim3(DP_THREADS), smem, s,
       (const bf16*)q, (const bf16*)k_store, (const bf16*)v_store, block_table, table_stride, row_slot, row_kv_len,
-      heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part, early);
+      heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part, early, (const bf16*)gate, gate_stride,
+      (bf16*)out, tail);
 }
 
 template <int QK, int VD>
@@ -625,17 +791,21 @@ int sb_diff_prefill(const void* q, const void* gate, int gate_stride, void* out,
 
 // One query row per sequence (its newest token, already in the cache): q [rows, heads * 2 * dim], out
 // [rows, heads * v_dim]; row_kv_len[r] counts the row's own key.  part: float scratch of
-// rows * heads * n_splits * 2 * (v_dim + 2).  Two launches (the walk, the merge).  early: see the kernel.
+// rows * heads * n_splits * 2 * (v_dim + 2), used with more than 8 parts or with cluster == 0: then two
+// launches (the walk, the merge), otherwise one (the parts are a thread-block cluster).  early: see the
+// kernel.  Returns 0, or 1 when it took two launches.
 int sb_diff_decode(const void* q, const void* gate, int gate_stride, void* out, const void* k_store,
                    const void* v_store, const int* block_table, int table_stride, const int* row_slot,
                    const int* row_kv_len, int rows, int heads, int kv_heads, int dim, int v_dim, float scale,
                    int window, float lambda, float out_scale, float eps, int n_splits, float* part, int early,
-                   cudaStream_t s) {
+                   int cluster, cudaStream_t s) {
   if (rows == 0) return 0;
   if (kv_heads <= 0 || heads % kv_heads || !sb_diff_prefill_takes(dim, v_dim) || n_splits < 1 || n_splits > 65535) return -2;
   int rc = -2;
+  bool finished = false;
+  DiffPrefillTail tail = {lambda, out_scale, eps};
 #define ARGS q, k_store, v_store, block_table, table_stride, row_slot, row_kv_len, rows, heads, kv_heads, scale, window, \
-             n_splits, part, early, s
+             n_splits, part, early, gate, gate_stride, out, tail, cluster, &finished, s
 #define BY_V(QK) switch (v_dim) { case 32: rc = launch_decode<QK, 32>(ARGS); break; case 64: rc = launch_decode<QK, 64>(ARGS); break; \
                                   case 128: rc = launch_decode<QK, 128>(ARGS); break; default: return -2; } break;
   switch (dim) {
@@ -651,11 +821,12 @@ int sb_diff_decode(const void* q, const void* gate, int gate_stride, void* out, 
   }
 #undef BY_V
 #undef ARGS
-  if (rc != 0) return rc;
-  DiffPrefillTail tail = {lambda, out_scale, eps};
+  if (rc != 0) return rc > 0 ? rc + 1 : rc;      // a CUDA error code, kept apart from "two launches"
+  if (finished) return 0;
   const int threads = v_dim >= 128 ? 128 : 64;
-  return launch_dependent(diff_decode_merge_kernel, dim3(rows * heads), dim3(threads), 0, s, (const float*)part,
-                          (const bf16*)gate, gate_stride, (bf16*)out, heads, v_dim, n_splits, tail);
+  rc = launch_dependent(diff_decode_merge_kernel, dim3(rows * heads), dim3(threads), 0, s, (const float*)part,
+                        (const bf16*)gate, gate_stride, (bf16*)out, heads, v_dim, n_splits, tail);
+  return rc == 0 ? 1 : rc > 0 ? rc + 1 : rc;
 }
 
 }  // extern "C"

@@ -842,6 +842,8 @@ def dynamic_tanh(x, alpha, weight, bias, delta=None, rows=None):
 DIFF_MAX_ROW = 256
 #: from this many tokens of one sequence in a step the tensor-core kernel is used
 DIFF_PREFILL_MIN_Q = 16
+#: up to this many parts of a row's keys are one thread-block cluster in the single-token kernel
+DIFF_CLUSTER_PARTS = 8
 
 
 def diff_prefill_takes(dtype, dim: int, v_dim: int) -> bool:
@@ -987,12 +989,16 @@ def diff_attention(q, gate, k_store, v_store, block_table, tok_slot, tok_pos, he
 
 
 def diff_attention_decode(q, gate, k_store, v_store, block_table, row_slot, row_kv_len, heads, kv_heads, dim, v_dim,
-                          scale, lam, out_scale, eps, window=None, n_splits=None, kv_hint=0, early=False):
+                          scale, lam, out_scale, eps, window=None, n_splits=None, kv_hint=0, early=False,
+                          cluster=True):
     """``diff_attention`` for one new token per sequence, on tensor cores (bfloat16): the query heads
     of a key/value head are the MMA's rows, so a page is read once for all of them and both maps;
     each row's keys are cut into ``n_splits`` parts (chosen from ``kv_hint``, the longest sequence,
-    so that the blocks fill the GPU) that a second kernel joins.  Row ``i`` is the newest token of the
-    sequence in ``row_slot[i]``, already in the cache; ``row_kv_len[i]`` counts it.
+    so that the blocks fill the GPU).  Up to ``DIFF_CLUSTER_PARTS`` parts are the blocks of one
+    thread-block cluster and join through distributed shared memory in the same launch (``cluster``
+    false: never); more leave their results in scratch memory and a second kernel joins them.  Row
+    ``i`` is the newest token of the sequence in ``row_slot[i]``, already in the cache;
+    ``row_kv_len[i]`` counts it.
 
     ``early``: the caller vouches that ``row_kv_len``, the page table and every cached key and value
     but the newest token's were complete before this step's first kernel started (``embedding(...,
@@ -1008,17 +1014,26 @@ def diff_attention_decode(q, gate, k_store, v_store, block_table, row_slot, row_
     if n_splits is None:
         blocks = rows * kv_heads * (-(-(heads // kv_heads) // 16))
         pages = max(1, -(-kv_hint // PAGE_TOKENS))
-        # measured at 2,048 keys: a part wants seven pages or more (shorter parts pay the ring's start
-        # and the merge for too little streaming), and all blocks resident at once (two fit on an SM)
-        n_splits = max(1, min(pages // 7, (2 * 148) // max(blocks, 1), 64))
+        # measured at 512 to 8,192 keys: all blocks resident at once (two fit on an SM); parts that join
+        # inside a cluster want about three pages or more, parts that join through scratch memory and a
+        # second launch seven (shorter ones pay the ring's start and the merge for too little
+        # streaming), and those are worth it only when they are at least three times as many
+        resident = (2 * 148) // max(blocks, 1)
+        n_splits = max(1, min((pages + 1) // 3, resident, DIFF_CLUSTER_PARTS if cluster else 1))
+        through_scratch = max(1, min(pages // 7, resident, 64))
+        if through_scratch >= 3 * n_splits:
+            n_splits = through_scratch
     out = torch.empty((rows, heads * v_dim), dtype=q.dtype, device=q.device)
-    part = torch.empty((rows * heads * n_splits * 2 * (v_dim + 2),), dtype=torch.float32, device=q.device)
+    part = None
+    if not cluster or n_splits > DIFF_CLUSTER_PARTS:
+        part = torch.empty((rows * heads * n_splits * 2 * (v_dim + 2),), dtype=torch.float32, device=q.device)
     rc = _lib("attention_diff_prefill").sb_diff_decode(
         _ptr(q), _ptr(gate), int(gate_stride), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
         block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, dim, v_dim,
         ctypes.c_float(scale), int(window or 0), ctypes.c_float(lam), ctypes.c_float(out_scale), ctypes.c_float(eps),
-        int(n_splits), _ptr(part), int(bool(early) and EARLY_READS), _stream())
-    _check(rc, "diff_attention_decode", 2)
+        int(n_splits), _ptr(part), int(bool(early) and EARLY_READS), int(bool(cluster)), _stream())
+    # 0: one launch; 1: two (walk and merge); above: a CUDA error code plus one
+    _check(rc - 1 if rc > 1 else 0 if rc == 1 else rc, "diff_attention_decode", 2 if rc == 1 else 1)
     return out
 
 

@@ -276,8 +276,10 @@ def test_prompt_attention_on_tensor_cores_alone(heads, groups, dim, vdim):
                                                       (40, 2, 16, 128), (2, 2, 128, 128)])
 def test_single_token_attention_on_tensor_cores_alone(heads, groups, dim, vdim):
     """Rows of unequal lengths in one launch (1 key, a page less one, a page, a page and one, 700),
-    every number of parts from one to more than there are pages, a key far back and the newest made
-    to stand out, with and without a window; 20 heads on one key/value head take two chunks of rows."""
+    every number of parts from one to more than there are pages (up to eight joined inside a
+    thread-block cluster, more, or all when told so, through scratch memory and a second kernel), a
+    key far back and the newest made to stand out, with and without a window; 20 heads on one
+    key/value head take two chunks of rows."""
     from starter_b200 import ops
 
     t = torch.bfloat16
@@ -301,10 +303,12 @@ def test_single_token_attention_on_tensor_cores_alone(heads, groups, dim, vdim):
             qs[r:r + 1, h, 0], qs[r:r + 1, h, 1], pages.k[:, h // (heads // groups), 0], pages.k[:, h // (heads // groups), 1],
             pages.v[:, h // (heads // groups)], scale, lam, lam0, eps, torch.tensor([n - 1]), window)[0]
             for h in range(heads)]) for r, n in enumerate(lengths)]) * torch.sigmoid(gs)
-        for splits in (1, 2, 3, 11, 16, None):
+        for splits, cluster in ((1, True), (1, False), (2, True), (3, True), (3, False), (5, True), (8, True),
+                                (8, False), (11, True), (16, True), (None, True)):
             got = ops.diff_attention_decode(qd, gd, ks, vs, table, i32([1] * len(lengths)), i32(lengths), heads, groups,
-                                            dim, vdim, scale, lam, 1 - lam0, eps, window, n_splits=splits, kv_hint=700)
-            close(got, want, "bfloat16", f"{splits} parts, window {window}", bf16=2.5e-2)
+                                            dim, vdim, scale, lam, 1 - lam0, eps, window, n_splits=splits, kv_hint=700,
+                                            cluster=cluster)
+            close(got, want, "bfloat16", f"{splits} parts, cluster {cluster}, window {window}", bf16=2.5e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
