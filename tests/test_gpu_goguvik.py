@@ -421,6 +421,35 @@ def test_prompt_then_tokens_one_by_one(tmp_path_factory, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["GA", "GD"])
+def test_long_decoding_over_many_pages(tmp_path_factory, name, dtype):
+    """Two requests of unequal lengths decoded together for 420 steps: the longer one grows from one
+    page to nine, so the single-token kernel goes from one part to several that join inside a cluster,
+    and the shorter one ends on the way; every logit is held to the plain statement."""
+    from starter_b200.engine import StepEntry
+
+    _, cfg, w = case(tmp_path_factory, name)
+    runner = runner_for(tmp_path_factory, name, dtype)
+    lengths, heads = (560, 190), (140, 3)
+    prompts = [random_prompt(n, cfg["vocab"], 300 + n) for n in lengths]
+    want = [plain.plain_forward(cfg, w, p) for p in prompts]
+    slots = [runner.open_sequence() for _ in prompts]
+    first = runner.step([StepEntry(s, p[:h], all_places(h)) for s, p, h in zip(slots, prompts, heads)])
+    got = [[first[:heads[0]]], [first[heads[0]:]]]
+    at = list(heads)
+    while at[0] < lengths[0]:
+        live = [i for i in range(2) if at[i] < lengths[i]]
+        rows = runner.step([StepEntry(slots[i], [prompts[i][at[i]]], [0]) for i in live])
+        for k, i in enumerate(live):
+            got[i].append(rows[k:k + 1])
+            at[i] += 1
+            if at[i] == lengths[i]:
+                runner.close_sequence(slots[i])
+    for i in range(2):
+        assert_close(torch.cat(got[i]), want[i], dtype, f"{name} request {i} decoded to {lengths[i]}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", CONFIGS)
 def test_portions_of_several_sizes(tmp_path_factory, name, dtype):
     from starter_b200.engine import StepEntry
