@@ -3,7 +3,7 @@
 The design: an embedding that is also the output head; layers of differential attention (two softmax
 maps per head over shared values, grouped key/value heads, no rotation, a query temperature that grows
 with the logarithm of the position, a sigmoid output gate, biased projections) and a dense gated
-feed-forward with the tanh form of gelu; Dynamic Tanh wherever another decoder norms; several residual
+feed-forward with tanh-approximated gelu; Dynamic Tanh wherever another decoder norms; several residual
 streams joined to the sublayers by hyper-connections; layers that attend over the keys and values an
 earlier layer cached instead of projecting their own.
 

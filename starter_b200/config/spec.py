@@ -28,7 +28,7 @@ class NormSpec:
 @dataclass(frozen=True)
 class DynamicTanhSpec:
     """Dynamic Tanh in a norm's place: ``tanh(alpha * x) * weight + bias`` with a scalar ``alpha``; it
-    computes no mean and no variance."""
+    takes no statistics of the row."""
 
     size: int
     kind: str = "dynamic_tanh"

@@ -44,7 +44,7 @@ __device__ __forceinline__ uint32_t pack_exact_bf16(float lo, float hi) {
 }
 
 // The activation of a gated feed-forward, chosen by the code the entry points take as `gated`:
-// 1: silu, g * sigmoid(g); 2: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))),
+// 1: silu, g * sigmoid(g); 2: tanh-approximated gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))),
 // which equals g * sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3)).  The fast forms (a few float ulp off) are
 // for results that are rounded to bfloat16 at once; the 32-bit path uses the exact ones.
 #define SB_ACT_SILU 1

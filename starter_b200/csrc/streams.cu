@@ -6,7 +6,7 @@
 //
 //     u    = sum_s in[s] * x_s                       the sublayer's input, before its norm
 //     y    = sublayer(norm(u))
-//     x_t <- sum_s mix[s][t] * x_s + out[t] * y      all t at once, from the old x
+//     x_t <- sum_s mix[s][t] * x_s + out[t] * y      every t from the x before the update
 //
 // The update that closes one sublayer and the read that opens the next touch the same S rows, so
 // they are ONE kernel here (as the residual sum and the norm after it are one kernel in the

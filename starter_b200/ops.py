@@ -772,8 +772,8 @@ def hyper_step(streams, dtype, pending=None, read=None, norm=None, rows=None):
     """One kernel around a sublayer of a model with several residual streams (float32 ``[T, S, H]``).
 
     ``pending = (y, mix, out, bias)``: the output ``y`` ``[T, H]`` of the sublayer before (``bias``
-    float32 ``[H]`` or None is added to it), which updates the streams, all at once from the old
-    ones, to ``x_t = sum_s mix[s, t] * x_s + out[t] * y``.  ``read``: float32 ``[S]``, the weights of
+    float32 ``[H]`` or None is added to it), which updates the streams, each from the
+    values before the update, to ``x_t = sum_s mix[s, t] * x_s + out[t] * y``.  ``read``: float32 ``[S]``, the weights of
     the sum ``u = sum_s read[s] * x_s`` that is returned (None: the plain sum of the streams).
     ``norm = (alpha, weight, bias)`` makes it ``tanh(alpha * u) * weight + bias`` (Dynamic Tanh); None
     returns ``u``.  The result is ``[T, H]`` in ``dtype``.  With ``rows`` (int32 ``[R]``) only those rows

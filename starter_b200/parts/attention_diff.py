@@ -87,7 +87,7 @@ class DifferentialAttention(Part):
                 parts += [params["k_bias"].float(), params["v_bias"].float()]
             self.bias = torch.cat(parts).contiguous()
             self.deferred_bias = params["o_bias"].float().contiguous()
-        # lambda is one number for the layer, formed in float32 as the vectors are
+        # a single lambda serves every head of the layer; it is formed in float32, as its vectors are
         f = lambda name: params[name].float()  # noqa: E731
         lam = torch.exp((f("lq1") * f("lk1")).sum()) - torch.exp((f("lq2") * f("lk2")).sum())
         self.lam = float(lam.item()) + float(s.lambda_init)

@@ -1,4 +1,4 @@
-"""Dense gated feed-forward: ``down(round(act(gate(x))) * up(x))`` with silu or the tanh form of gelu,
+"""Dense gated feed-forward: ``down(round(act(gate(x))) * up(x))`` with silu or tanh-approximated gelu,
 no biases, no routing."""
 
 from __future__ import annotations

@@ -3,7 +3,7 @@
 A token has ``S`` streams ``x_1 .. x_S`` (float32 ``[tokens, S, hidden]``), all equal to its embedding
 at the start.  A sublayer with this part's ``in`` ``[S]``, ``out`` ``[S]`` and ``mix`` ``[S, S]``
 (indexed ``[from, to]``) reads ``u = sum_s in[s] * x_s``, computes ``y = sublayer(norm(u))`` and
-updates every stream at once from the old ones: ``x_t = sum_s mix[s, t] * x_s + out[t] * y``.  The
+writes every stream from the values before the update: ``x_t = sum_s mix[s, t] * x_s + out[t] * y``.  The
 model's output is the sum of the streams.
 
 The update that closes a sublayer and the read (and norm) that opens the next are one kernel

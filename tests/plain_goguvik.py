@@ -56,7 +56,7 @@ def plain_stream_read(streams, read):
 
 
 def plain_stream_write(streams, y, mix, out):
-    """All streams at once from the old ones: new[t] = sum_s mix[s, t] old[s] + out[t] y."""
+    """Every new stream from the values before the update: new[t] = sum_s mix[s, t] old[s] + out[t] y."""
     return torch.einsum("sk,tsw->tkw", mix, streams) + out[None, :, None] * y[:, None, :]
 
 

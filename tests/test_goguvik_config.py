@@ -99,7 +99,7 @@ def test_plain_streams_with_identity_mixing_are_a_residual_sum():
     y = torch.randn(5, 7, dtype=torch.float64)
     new = plain.plain_stream_write(t, y, torch.eye(3, dtype=torch.float64), torch.tensor([1.0, 0.0, 2.0], dtype=torch.float64))
     assert torch.allclose(new[:, 0], t[:, 0] + y) and torch.allclose(new[:, 1], t[:, 1]) and torch.allclose(new[:, 2], t[:, 2] + 2 * y)
-    # the matrix is indexed [from, to]: a single entry [0, 2] copies stream 0 into stream 2
+    # rows of the matrix are source streams, columns destinations: the entry [0, 2] copies stream 0 into stream 2
     mix = torch.zeros(3, 3, dtype=torch.float64)
     mix[0, 2] = 1.0
     moved = plain.plain_stream_write(t, torch.zeros_like(y), mix, torch.zeros(3, dtype=torch.float64))
