@@ -11,6 +11,7 @@ import json
 import os
 
 from .goguvik import GoguvikConfig
+from .kesedra import KesedraConfig
 from .qwen3 import ConfigError, Qwen3Config
 
 ARCHITECTURES: dict = {}
@@ -25,6 +26,7 @@ def register_architecture(name: str, config_cls) -> None:
 
 register_architecture(Qwen3Config.architecture, Qwen3Config)
 register_architecture(GoguvikConfig.architecture, GoguvikConfig)
+register_architecture(KesedraConfig.architecture, KesedraConfig)
 
 
 def architecture_name(raw: dict):

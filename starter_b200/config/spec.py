@@ -18,11 +18,13 @@ from typing import Optional
 
 @dataclass(frozen=True)
 class NormSpec:
-    """Root-mean-square norm with a plain gain (no ``1 + w``)."""
+    """Root-mean-square norm ``x / sqrt(mean(x^2) + eps) * gain``.  ``unit_offset`` false: the stored
+    weight is the gain; true: the weight is stored around zero and the gain is ``1 + weight``."""
 
     size: int
     eps: float
     kind: str = "rmsnorm"
+    unit_offset: bool = False
 
 
 @dataclass(frozen=True)
@@ -41,6 +43,16 @@ class RopeSpec:
     head_dim: int
     theta: float
     kind: str = "rope"
+
+
+@dataclass(frozen=True)
+class InterleavedRopeSpec:
+    """Rotary positions that turn entry ``2i`` with entry ``2i + 1`` of the first ``dims`` entries of a
+    vector by the angle ``position * base ** (-2i / dims)``; entries from ``dims`` on pass unchanged."""
+
+    dims: int
+    base: float
+    kind: str = "rope_interleaved"
 
 
 @dataclass(frozen=True)
@@ -103,6 +115,76 @@ class DifferentialAttentionSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are up-projections of one cached low-rank latent per token.
+
+    Queries: ``W_uq`` of the RMS-normed ``q_rank`` latent ``W_dq h``; a head's query has ``head_dim`` plain
+    and ``rot_dim`` rotated entries.  Keys and values: ``W_dkv h`` gives ``kv_rank`` entries, RMS-normed
+    into the latent ``c``, and ``rot_dim`` more, rotated, that all heads share as the rotated key part; a
+    head's plain key is ``W_uk c``, its value ``W_uv c`` (``value_dim`` entries).  The cache holds ``c``
+    and the rotated part.  ``window``: a query sees itself and the ``window - 1`` tokens before it (None:
+    all).  ``own_kv`` false: no ``W_dkv``; the layer reads the cache entry of another layer (the run order
+    says which) with its own ``W_uk`` and ``W_uv``.  The inner norms have plain gains."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    value_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    norm_eps: float
+    position: Optional[InterleavedRopeSpec]
+    window: Optional[int] = None
+    own_kv: bool = True
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class WkvSpec:
+    """A linear recurrence with a ``head_dim x head_dim`` state per head (the time mixing of the RWKV
+    family): receptance, key, value, gate and decay each read their own mix of the token's input and the
+    previous token's; the decay of a key channel is ``exp(-exp(w2 tanh(w1 mix) + w0))`` with a low-rank
+    ``w1``/``w2`` of ``decay_rank``; the current token's ``k v^T`` enters its own output through a bonus
+    vector; each head's output is divided by its root mean square (``norm_eps``), scaled by a gain and by
+    ``silu`` of the gate."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    decay_rank: int
+    norm_eps: float
+    kind: str = "wkv"
+
+
+@dataclass(frozen=True)
+class BiasedFeedForwardSpec:
+    """Dense feed-forward with biases on both projections: ``down(act(up(x) + b_up)) + b_down``;
+    ``activation`` ``"relu2"`` is the square of relu."""
+
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "relu2"
+    kind: str = "dense_biased"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of ``experts`` small gated feed-forwards without biases, of which a token uses the ``top``
+    with the largest router logits (``router(x) + bias`` in 32-bit), weighted by the softmax over those
+    logits alone.  An expert: ``down(g * sigmoid(1.702 g) * (u + 1))`` with ``g = min(gate(x), limit)``,
+    ``u = clamp(up(x), -limit, limit)``."""
+
+    hidden_size: int
+    intermediate_size: int
+    experts: int
+    top: int
+    limit: float
+    kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
 class HyperConnectionSpec:
     """How one sublayer reads from and writes to ``streams`` residual streams: ``in`` and ``out``
     vectors of that length and a ``[from, to]`` mixing matrix."""
@@ -153,6 +235,16 @@ def hyper_layer(mixer, feed_forward, norm1, norm2, connection, names) -> LayerSp
                       "connection1": connection, "connection2": connection}, names, "hyper_prenorm")
 
 
+def sandwich_layer(mixer, feed_forward, norm, names) -> LayerSpec:
+    """A layer with a norm in front of and behind each sublayer, around a float32 residual stream:
+    ``x + norm1b(mixer(norm1(x)))``, then ``+ norm2b(feed_forward(norm2(.)))``; ``feed_forward`` None: the
+    layer is its mixer alone."""
+    if feed_forward is None:
+        return LayerSpec({"mixer": mixer, "norm1": norm, "norm1b": norm}, names, "sandwich_mixer_only")
+    return LayerSpec({"mixer": mixer, "feed_forward": feed_forward, "norm1": norm, "norm1b": norm,
+                      "norm2": norm, "norm2b": norm}, names, "sandwich")
+
+
 def prenorm_layer(mixer, feed_forward, norm1, norm2, names, arrangement: str = "prenorm") -> LayerSpec:
     """The layer of the pre-norm block: ``x + mixer(norm1(x))``, then ``+ feed_forward(norm2(.))``."""
     return LayerSpec({"mixer": mixer, "feed_forward": feed_forward, "norm1": norm1, "norm2": norm2},
@@ -198,6 +290,8 @@ class ModelSpec:
     final_norm_names: Optional[dict] = None
     #: checkpoint tensors that may be there and are not read
     ignored_tensors: tuple = ()
+    #: what a token's embedding is multiplied by (models whose residual stream is float32)
+    embedding_scale: float = 1.0
 
     def cache_entries(self) -> int:
         return 1 + max((e.cache for e in self.schedule), default=-1)

@@ -1,0 +1,375 @@
+// A routed mixture of small gated feed-forward experts, for any number of tokens, without a word
+// from the host between its kernels (so that it can sit inside a captured step).
+//
+//   route    z = W_r h + b in float; the `top` largest (the lower index first among equals); their
+//            weights are the softmax over those `top` logits alone.
+//   align    the (token, choice) pairs grouped by expert: every expert's pairs fill whole tiles of
+//            MOE_BM rows (padded with -1), `tile_expert` names each tile's expert, `n_tiles` counts them.
+//   up       per tile: g = min(gate(h), limit), u = clamp(up(h), -limit, limit),
+//            a = g * sigmoid(1.702 g) * (u + 1), for the tile's rows gathered from h.
+//   down     per tile: the expert's down projection of a, filed at the pair's own place.
+//   combine  out[t] = sum_c weight[t][c] * down[t][c], summed in float in the order of the choices.
+//
+// Products accumulate in float; gate and up are rounded to the working type before the activation, as
+// the projections of the dense feed-forward are.  A token's result depends on nothing but its own row
+// and the experts' weights: not on which tile it landed in, nor on who else is in the step.
+#include <mma.h>
+
+#include "common.cuh"
+
+#define MOE_BM 32
+#define MOE_BN 64
+#define MOE_BK 32
+#define MOE_MAX_EXPERTS 1024
+#define MOE_MAX_TOP 16
+
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w, const float* __restrict__ b,
+                                 int* __restrict__ ids, float* __restrict__ weights, int width, int experts, int top) {
+  extern __shared__ float z[];
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(h);
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const T* hr = h + (size_t)row * width;
+  for (int e = warp; e < experts; e += warps) {
+    const float* wr = w + (size_t)e * width;
+    float a = 0.f;
+    for (int c = lane; c < width; c += 32) a += to_f<T>(hr[c]) * wr[c];
+    a = warp_sum(a);
+    if (lane == 0) z[e] = a + (b ? b[e] : 0.f);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float best[MOE_MAX_TOP];
+    float top_max = 0.f;
+    for (int c = 0; c < top; ++c) {
+      // the largest logit left, the lowest index among equals
+      float v = -INFINITY;
+      int at = 0x7fffffff;
+      for (int e = lane; e < experts; e += 32)
+        if (z[e] > v) { v = z[e]; at = e; }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ov > v || (ov == v && oa < at)) { v = ov; at = oa; }
+      }
+      if (at >= experts) at = 0;          // no finite logit left: keep the indices inside the table
+      if (c == 0) top_max = v;
+      best[c] = v;
+      if (lane == 0) {
+        ids[(size_t)row * top + c] = at;
+        z[at] = -INFINITY;
+      }
+      __syncwarp();
+    }
+    if (lane == 0) {
+      float sum = 0.f;
+      for (int c = 0; c < top; ++c) {
+        best[c] = expf(best[c] - top_max);
+        sum += best[c];
+      }
+      for (int c = 0; c < top; ++c) weights[(size_t)row * top + c] = best[c] / sum;
+    }
+  }
+}
+
+// One block.  ids: [n_pairs]; sorted: [capacity] receives pair numbers or -1; tile_expert: [max_tiles].
+__global__ void moe_align_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ sorted,
+                                 int capacity, int* __restrict__ tile_expert, int* __restrict__ n_tiles) {
+  __shared__ int count[MOE_MAX_EXPERTS], offset[MOE_MAX_EXPERTS], total;
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(ids);
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0, tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      offset[e] = off;
+      const int nt = (count[e] + MOE_BM - 1) / MOE_BM;
+      for (int t = 0; t < nt; ++t) tile_expert[tiles++] = e;
+      off += nt * MOE_BM;
+      count[e] = 0;
+    }
+    n_tiles[0] = tiles;
+    total = off;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < total && i < capacity; i += blockDim.x) sorted[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];
+    sorted[offset[e] + atomicAdd(&count[e], 1)] = i;
+  }
+}
+
+// A tile of MOE_BM rows times MOE_BN outputs in float on the CUDA cores: the 32-bit path, and the
+// working-type path for widths the tensor-core kernel does not take.  UP: rows gathered from h by
+// pair / top, two weight blocks (gate, up) and the activation; else rows of `a`, one block, results
+// filed by pair.
+template <typename T, bool UP>
+__global__ void __launch_bounds__(256)
+moe_tile_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, const int* __restrict__ sorted,
+                const int* __restrict__ tile_expert, const int* __restrict__ n_tiles, int k_dim, int n_out, int top,
+                float limit) {
+  __shared__ float xs[MOE_BM][MOE_BK + 1];
+  __shared__ float ws[UP ? 2 : 1][MOE_BN][MOE_BK + 1];
+  __shared__ int src[MOE_BM];
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(x);
+  SB_BEHIND_WAIT(sorted);
+  SB_BEHIND_WAIT(tile_expert);
+  SB_BEHIND_WAIT(n_tiles);
+  const int tile = blockIdx.x;
+  if (tile >= n_tiles[0]) return;
+  const int e = tile_expert[tile];
+  const int n0 = blockIdx.y * MOE_BN;
+  const int tid = threadIdx.x;
+  if (tid < MOE_BM) src[tid] = sorted[tile * MOE_BM + tid];
+  __syncthreads();
+  const T* we = w + (size_t)e * (UP ? 2 : 1) * n_out * k_dim;
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[UP ? 2 : 1][2][4];
+#pragma unroll
+  for (int a = 0; a < (UP ? 2 : 1); ++a)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[a][i][j] = 0.f;
+  for (int k0 = 0; k0 < k_dim; k0 += MOE_BK) {
+    for (int i = tid; i < MOE_BM * MOE_BK; i += 256) {
+      const int m = i / MOE_BK, kk = i % MOE_BK;
+      const int pair = src[m];
+      float v = 0.f;
+      if (pair >= 0 && k0 + kk < k_dim) {
+        const size_t row = UP ? (size_t)(pair / top) : (size_t)tile * MOE_BM + m;
+        v = to_f<T>(x[row * k_dim + k0 + kk]);
+      }
+      xs[m][kk] = v;
+    }
+    for (int i = tid; i < (UP ? 2 : 1) * MOE_BN * MOE_BK; i += 256) {
+      const int a = i / (MOE_BN * MOE_BK), rem = i % (MOE_BN * MOE_BK);
+      const int n = rem / MOE_BK, kk = rem % MOE_BK;
+      float v = 0.f;
+      if (n0 + n < n_out && k0 + kk < k_dim) v = to_f<T>(we[((size_t)a * n_out + n0 + n) * k_dim + k0 + kk]);
+      ws[a][n][kk] = v;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < MOE_BK; ++kk) {
+      const float x0 = xs[ty * 2][kk], x1 = xs[ty * 2 + 1][kk];
+#pragma unroll
+      for (int a = 0; a < (UP ? 2 : 1); ++a)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float wv = ws[a][tx + 16 * j][kk];
+          acc[a][0][j] += x0 * wv;
+          acc[a][1][j] += x1 * wv;
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int m = ty * 2 + i;
+    const int pair = src[m];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx + 16 * j;
+      if (n >= n_out) continue;
+      if (UP) {
+        float g = rnd<T>(acc[0][i][j]), u = rnd<T>(acc[UP ? 1 : 0][i][j]);
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        const float a = pair >= 0 ? g / (1.f + expf(-1.702f * g)) * (u + 1.f) : 0.f;
+        y[((size_t)tile * MOE_BM + m) * n_out + n] = from_f<T>(a);
+      } else if (pair >= 0) {
+        y[(size_t)pair * n_out + n] = from_f<T>(acc[0][i][j]);
+      }
+    }
+  }
+}
+
+// The same tiles on the tensor cores (bfloat16, k and n_out multiples of 16): four warps, each a 16 x 32
+// (rows x outputs) piece of the 32 x 64 tile, wmma 16 x 16 x 16 with float accumulators; operands are
+// staged in shared memory, where the gathered rows become contiguous.
+template <bool UP>
+__global__ void __launch_bounds__(128)
+moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                   const int* __restrict__ sorted, const int* __restrict__ tile_expert,
+                   const int* __restrict__ n_tiles, int k_dim, int n_out, int top, float limit) {
+  using namespace nvcuda;
+  constexpr int BK = 64, LD = BK + 8;
+  __shared__ __align__(32) bf16 xs[MOE_BM][LD];
+  __shared__ __align__(32) bf16 ws[UP ? 2 : 1][MOE_BN][LD];
+  __shared__ __align__(32) float cs[UP ? 2 : 1][MOE_BM][MOE_BN + 4];
+  __shared__ int src[MOE_BM];
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(x);
+  SB_BEHIND_WAIT(sorted);
+  SB_BEHIND_WAIT(tile_expert);
+  SB_BEHIND_WAIT(n_tiles);
+  const int tile = blockIdx.x;
+  if (tile >= n_tiles[0]) return;
+  const int e = tile_expert[tile];
+  const int n0 = blockIdx.y * MOE_BN;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid < MOE_BM) src[tid] = sorted[tile * MOE_BM + tid];
+  __syncthreads();
+  const bf16* we = w + (size_t)e * (UP ? 2 : 1) * n_out * k_dim;
+  const int wm = warp >> 1, wn = warp & 1;
+  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[UP ? 2 : 1][2];
+#pragma unroll
+  for (int a = 0; a < (UP ? 2 : 1); ++a)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) wmma::fill_fragment(acc[a][j], 0.f);
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int k0 = 0; k0 < k_dim; k0 += BK) {
+    // 16-byte pieces: 8 bfloat16 (k_dim is a multiple of 16, so a piece is inside the row or outside it)
+    for (int i = tid; i < MOE_BM * (BK / 8); i += 128) {
+      const int m = i / (BK / 8), kk = (i % (BK / 8)) * 8;
+      const int pair = src[m];
+      uint4 v = zero;
+      if (pair >= 0 && k0 + kk < k_dim) {
+        const size_t row = UP ? (size_t)(pair / top) : (size_t)tile * MOE_BM + m;
+        v = *reinterpret_cast<const uint4*>(x + row * k_dim + k0 + kk);
+      }
+      *reinterpret_cast<uint4*>(&xs[m][kk]) = v;
+    }
+    for (int i = tid; i < (UP ? 2 : 1) * MOE_BN * (BK / 8); i += 128) {
+      const int a = i / (MOE_BN * (BK / 8)), rem = i % (MOE_BN * (BK / 8));
+      const int n = rem / (BK / 8), kk = (rem % (BK / 8)) * 8;
+      uint4 v = zero;
+      if (n0 + n < n_out && k0 + kk < k_dim)
+        v = *reinterpret_cast<const uint4*>(we + ((size_t)a * n_out + n0 + n) * k_dim + k0 + kk);
+      *reinterpret_cast<uint4*>(&ws[a][n][kk]) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fa;
+      wmma::load_matrix_sync(fa, &xs[wm * 16][kk], LD);
+#pragma unroll
+      for (int a = 0; a < (UP ? 2 : 1); ++a)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fb;
+          wmma::load_matrix_sync(fb, &ws[a][wn * 32 + j * 16][kk], LD);
+          wmma::mma_sync(acc[a][j], fa, fb, acc[a][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int a = 0; a < (UP ? 2 : 1); ++a)
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      wmma::store_matrix_sync(&cs[a][wm * 16][wn * 32 + j * 16], acc[a][j], MOE_BN + 4, wmma::mem_row_major);
+  __syncthreads();
+  for (int i = tid; i < MOE_BM * MOE_BN; i += 128) {
+    const int m = i / MOE_BN, nn = i % MOE_BN;
+    const int n = n0 + nn;
+    const int pair = src[m];
+    if (n >= n_out) continue;
+    if (UP) {
+      float g = rnd<bf16>(cs[0][m][nn]), u = rnd<bf16>(cs[UP ? 1 : 0][m][nn]);
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      const float a = pair >= 0 ? g / (1.f + expf(-1.702f * g)) * (u + 1.f) : 0.f;
+      y[((size_t)tile * MOE_BM + m) * n_out + n] = from_f<bf16>(a);
+    } else if (pair >= 0) {
+      y[(size_t)pair * n_out + n] = from_f<bf16>(cs[0][m][nn]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ down, const float* __restrict__ weights, T* __restrict__ out,
+                                   int width, int top) {
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(down);
+  SB_BEHIND_WAIT(weights);
+  const int row = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float a = 0.f;
+    for (int j = 0; j < top; ++j)
+      a += weights[(size_t)row * top + j] * to_f<T>(down[((size_t)row * top + j) * width + c]);
+    out[(size_t)row * width + c] = from_f<T>(a);
+  }
+}
+
+extern "C" {
+
+int sb_moe_tile_rows() { return MOE_BM; }
+int sb_moe_max_experts() { return MOE_MAX_EXPERTS; }
+int sb_moe_max_top() { return MOE_MAX_TOP; }
+
+// h: [n_tokens, width]; w: float [experts, width]; b: float [experts] or null; ids: int [n_tokens, top];
+// weights: float [n_tokens, top].
+int sb_moe_route(int dtype, const void* h, const float* w, const float* b, int* ids, float* weights, int n_tokens,
+                 int width, int experts, int top, cudaStream_t s) {
+  if (n_tokens == 0) return 0;
+  if (experts < 1 || experts > MOE_MAX_EXPERTS || top < 1 || top > MOE_MAX_TOP || top > experts) return -2;
+  const size_t smem = (size_t)experts * sizeof(float);
+  if (dtype == 0)
+    return launch_dependent(moe_route_kernel<float>, dim3(n_tokens), dim3(128), smem, s, (const float*)h, w, b, ids,
+                            weights, width, experts, top);
+  return launch_dependent(moe_route_kernel<bf16>, dim3(n_tokens), dim3(128), smem, s, (const bf16*)h, w, b, ids,
+                          weights, width, experts, top);
+}
+
+int sb_moe_align(const int* ids, int n_pairs, int experts, int* sorted, int capacity, int* tile_expert, int* n_tiles,
+                 cudaStream_t s) {
+  if (experts < 1 || experts > MOE_MAX_EXPERTS) return -2;
+  return launch_dependent(moe_align_kernel, dim3(1), dim3(256), 0, s, ids, n_pairs, experts, sorted, capacity,
+                          tile_expert, n_tiles);
+}
+
+// up != 0: x = h [n_tokens, k_dim], w = [experts, 2 * n_out, k_dim] (gate rows, then up rows), y =
+// [capacity, n_out] in the order of `sorted`.  up == 0: x = that y [capacity, k_dim], w = [experts,
+// n_out, k_dim], y = [n_pairs, n_out] by pair.
+int sb_moe_tiles(int dtype, int up, const void* x, const void* w, void* y, const int* sorted, const int* tile_expert,
+                 const int* n_tiles, int max_tiles, int k_dim, int n_out, int top, float limit, cudaStream_t s) {
+  if (max_tiles == 0) return 0;
+  const dim3 grid(max_tiles, (n_out + MOE_BN - 1) / MOE_BN);
+  if (dtype == 0) {
+    if (up)
+      return launch_dependent(moe_tile_kernel<float, true>, grid, dim3(256), 0, s, (const float*)x, (const float*)w,
+                              (float*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+    return launch_dependent(moe_tile_kernel<float, false>, grid, dim3(256), 0, s, (const float*)x, (const float*)w,
+                            (float*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+  }
+  const bool tc = k_dim % 16 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0);
+  if (tc) {
+    if (up)
+      return launch_dependent(moe_tile_tc_kernel<true>, grid, dim3(128), 0, s, (const bf16*)x, (const bf16*)w,
+                              (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+    return launch_dependent(moe_tile_tc_kernel<false>, grid, dim3(128), 0, s, (const bf16*)x, (const bf16*)w,
+                            (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+  }
+  if (up)
+    return launch_dependent(moe_tile_kernel<bf16, true>, grid, dim3(256), 0, s, (const bf16*)x, (const bf16*)w,
+                            (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+  return launch_dependent(moe_tile_kernel<bf16, false>, grid, dim3(256), 0, s, (const bf16*)x, (const bf16*)w,
+                          (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+}
+
+int sb_moe_combine(int dtype, const void* down, const float* weights, void* out, int n_tokens, int width, int top,
+                   cudaStream_t s) {
+  if (n_tokens == 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == 0)
+    return launch_dependent(moe_combine_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)down,
+                            weights, (float*)out, width, top);
+  return launch_dependent(moe_combine_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (const bf16*)down, weights,
+                          (bf16*)out, width, top);
+}
+
+}  // extern "C"

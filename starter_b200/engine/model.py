@@ -14,6 +14,7 @@ import torch
 from .. import ops
 from ..parts import ParamSpec, lookup
 from ..parts.hyper import close_rows
+from ..parts.sandwich import close_rows32
 
 
 def build_layers(spec, dtype, device):
@@ -101,6 +102,14 @@ class DecoderModel:
         self.many_streams = kinds == {True}
         if not self.many_streams and spec.streams != 1:
             raise ValueError(f"the spec asks for {spec.streams} residual streams but its layers keep one")
+        #: True when the layers keep the residual stream in float32 (norms on both sides of a sublayer)
+        kinds = {getattr(b, "residual_kind", None) == "float32" for b in self.blocks}
+        if len(kinds) > 1:
+            raise ValueError("layers with a float32 residual stream and layers with one of the working type "
+                             "cannot be mixed")
+        self.float_residual = kinds == {True}
+        if not self.float_residual and spec.embedding_scale != 1.0:
+            raise ValueError("an embedding scale needs layers that keep a float32 residual stream")
         for entry in spec.schedule:
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"the run order names layer {entry.layer}; the model has {len(self.blocks)}")
@@ -176,6 +185,8 @@ class DecoderModel:
         if self.many_streams:
             # several residual streams per token, float32, all equal to the embedding at the start
             residual = ops.embedding_streams(ctx.tokens, self.embed, self.spec.streams, ctx.status, fence=True)
+        elif self.float_residual:
+            residual = ops.embedding32(ctx.tokens, self.embed, self.spec.embedding_scale, ctx.status, fence=True)
         else:
             residual = ops.embedding(ctx.tokens, self.embed, ctx.status, fence=True)
         ctx.fenced = True
@@ -189,6 +200,8 @@ class DecoderModel:
         """Float32 logits ``[len(rows), vocab]`` of the rows asked for."""
         if self.many_streams:
             h = close_rows(residual, pending, rows, self.final_norm, self.dtype)
+        elif self.float_residual:
+            h = close_rows32(residual, pending, rows, self.final_norm, self.dtype)
         else:
             h = self.final_norm.add_rows(residual, pending, rows)
         return ops.linear(h, self.lm_head, out_float=True, status=status)

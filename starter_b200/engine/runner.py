@@ -60,6 +60,11 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0") -> DecoderMode
     device = require_cuda(device)
     dtype = resolve_dtype(dtype)
     config = load_config(model_dir)
+    if hasattr(config, "with_tensor_shapes"):
+        # a design may leave a size to the checkpoint: the config then takes it from the stored shapes
+        from ..weights.safetensors_io import open_model_files
+        config = config.with_tensor_shapes({name: tuple(handle.entries[name][1])
+                                            for name, handle in open_model_files(model_dir).items()})
     spec = config.to_model_spec()
     model = DecoderModel(spec, dtype, device)
     alias = (spec.lm_head_name, spec.embed_name) if spec.tie_embeddings else None

@@ -1278,3 +1278,296 @@ class OpenChain:
         if rc in (-3, -4):
             raise KernelError(f"the TMA descriptors for a chain could not be made (code {rc})")
         _check(rc, "dense_chain")
+
+
+# ---------------------------------------------------------------------------------------- a float32 residual stream
+
+def embedding32(tokens, table, scale=1.0, status=None, fence=False):
+    """``out[t] = float(table[tokens[t]]) * scale``: float32 ``[T, H]``, the start of a residual stream
+    that is kept in 32-bit whatever the working type.  ``fence`` as in ``embedding``."""
+    _need(tokens, "tokens", torch.int32, 1)
+    _need(table, "table", None, 2)
+    out = torch.empty((tokens.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+    rc = _lib("residual32").sb_embed32(
+        _code(table.dtype), _ptr(tokens), _ptr(table), _ptr(out), tokens.shape[0], table.shape[1],
+        table.shape[0], ctypes.c_float(scale), _ptr(status), int(fence), _stream())
+    _check(rc, "embedding32")
+    return out
+
+
+def residual_norm(x, dtype, eps, pending=None, next_gain=None, rows=None):
+    """One kernel between two sublayers of a model whose residual stream ``x`` is float32 ``[T, H]`` and
+    whose sublayers have a norm behind them as well as in front.
+
+    ``pending = (y, post_gain, bias, post_eps)``: the output ``y`` ``[T, H]`` (in ``dtype``) of the sublayer
+    before, with a float32 ``bias`` ``[H]`` still to be added to it (or None); it is RMS-normed with
+    ``post_gain`` (float32 ``[H]``; None: taken as it is) and ``post_eps`` and added onto ``x`` in place.  ``next_gain``
+    (float32 ``[H]``): the RMS norm of the new row is returned in ``dtype``; None: nothing is returned.
+    With ``rows`` (int32 ``[R]``) only those rows are computed, ``x`` is left as it was and the result is
+    ``[R, H]``.  Sums, norms and the row itself are float32; the gains are the factors themselves."""
+    _need(x, "x", torch.float32, 2)
+    n_tokens, hidden = x.shape
+    y = post = bias = None
+    post_eps = eps
+    if pending is not None:
+        y, post, bias, post_eps = pending
+        _need(y, "y", dtype, 2)
+        if tuple(y.shape) != (n_tokens, hidden):
+            raise KernelError(f"y {tuple(y.shape)} does not match the residual stream {tuple(x.shape)}")
+        if post is not None:
+            _f32(post, "post gain", (hidden,))
+        if bias is not None:
+            _f32(bias, "bias", (hidden,))
+    n_rows = n_tokens
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n_rows = rows.shape[0]
+    out = None
+    if next_gain is not None:
+        _f32(next_gain, "next gain", (hidden,))
+        out = torch.empty((n_rows, hidden), dtype=dtype, device=x.device)
+    rc = _lib("residual32").sb_residual_norm(
+        _code(dtype), _ptr(x), _ptr(y), _ptr(bias), _ptr(post), _ptr(next_gain), _ptr(out), _ptr(rows), n_rows,
+        hidden, ctypes.c_float(post_eps), ctypes.c_float(eps), _stream())
+    _check(rc, "residual_norm")
+    return out
+
+
+#: what ``bias_act`` can apply after the bias
+BIAS_ACTIVATIONS = {None: 0, "none": 0, "relu2": 1, "tanh": 2}
+
+
+def bias_act(x, bias=None, activation=None):
+    """``act(x + bias)`` for ``x`` ``[T, N]`` and a float32 ``bias`` ``[N]`` (or None); ``activation``:
+    None, ``"relu2"`` (the square of relu) or ``"tanh"``.  The sum and the activation are float."""
+    _need(x, "x", None, 2)
+    if activation not in BIAS_ACTIVATIONS:
+        raise KernelError(f"no activation {activation!r} here (known: relu2, tanh)")
+    if bias is not None:
+        _f32(bias, "bias", (x.shape[1],))
+    out = torch.empty_like(x)
+    rc = _lib("residual32").sb_bias_act(_code(x.dtype), _ptr(x), _ptr(bias), _ptr(out), x.shape[0], x.shape[1],
+                                        BIAS_ACTIVATIONS[activation], _stream())
+    _check(rc, "bias_act")
+    return out
+
+
+# ---------------------------------------------------------------------------------------- recurrence with a matrix state
+
+def wkv_max_dim() -> int:
+    return _lib("wkv").sb_wkv_max_dim()
+
+
+def token_shift(h, state, mu, tok_slot):
+    """``out[s] = h + (previous(h) - h) * mu[s]`` for each of the ``mu`` ``[S, W]`` (float32): ``[S, T, W]`` in
+    the type of ``h`` ``[T, W]``.  A row's predecessor is the row before it when that belongs to the same
+    sequence, else the first ``W`` floats of its slot's ``state`` (float32 ``[slots, N]``): what the
+    sequence's last token left there, zeros for a sequence that starts."""
+    _need(h, "h", None, 2)
+    _need(state, "state", torch.float32, 2)
+    _need(mu, "mu", torch.float32, 2)
+    _need(tok_slot, "tok_slot", torch.int32, 1)
+    n_tokens, width = h.shape
+    if mu.shape[1] != width or state.shape[1] < width:
+        raise KernelError(f"mu {tuple(mu.shape)} / state {tuple(state.shape)} do not fit rows of {width}")
+    out = torch.empty((mu.shape[0], n_tokens, width), dtype=h.dtype, device=h.device)
+    rc = _lib("wkv").sb_token_shift(_code(h.dtype), _ptr(h), _ptr(state), ctypes.c_longlong(state.shape[1]), _ptr(mu),
+                                    _ptr(out), _ptr(tok_slot), n_tokens, width, mu.shape[0], _stream())
+    _check(rc, "token_shift")
+    return out
+
+
+def wkv_scan(r, k, v, x_decay, w0, u, g, gain, state, h, seq_slot, seq_q_start, seq_q_len, heads, dim, eps):
+    """The recurrence ``o_t = (S + diag(u) k_t v_t^T)^T r_t``, ``S <- diag(w_t) S + k_t v_t^T`` with
+    ``w_t = exp(-exp(x_decay_t + w0))`` per head over the sequences of a step, followed by the head's
+    unit norm, ``gain`` and ``silu(g)``.
+
+    ``r, k, v, g`` ``[T, heads * dim]`` in the working type; ``x_decay`` float32 of that shape; ``w0``,
+    ``gain`` float32 ``[heads * dim]``; ``u`` float32 ``[heads, dim]``.  ``state`` float32 ``[slots, W +
+    heads * dim * dim]``: each slot's last mixer input (``h``'s row, ``W`` floats, written here for the
+    sequence's last token of this step) and its ``S``, read at the start and written at the end.
+    Returns ``[T, heads * dim]`` in the working type."""
+    _need(r, "r", None, 2)
+    n_tokens = r.shape[0]
+    hd = heads * dim
+    for name, t in (("k", k), ("v", v), ("g", g)):
+        _need(t, name, r.dtype, 2)
+        if tuple(t.shape) != (n_tokens, hd):
+            raise KernelError(f"{name} has shape {tuple(t.shape)}, expected {(n_tokens, hd)}")
+    if r.shape[1] != hd:
+        raise KernelError(f"r has width {r.shape[1]}, expected {hd}")
+    _f32(x_decay, "x_decay", (n_tokens, hd))
+    _f32(w0, "w0", (hd,))
+    _f32(gain, "gain", (hd,))
+    _need(u, "u", torch.float32)
+    if u.numel() != hd:
+        raise KernelError(f"u has {u.numel()} entries, expected {hd}")
+    _need(h, "h", r.dtype, 2)
+    width = h.shape[1]
+    _need(state, "state", torch.float32, 2)
+    if state.shape[1] != width + heads * dim * dim:
+        raise KernelError(f"a slot's state has {state.shape[1]} floats, expected {width + heads * dim * dim}")
+    for name, t in (("seq_slot", seq_slot), ("seq_q_start", seq_q_start), ("seq_q_len", seq_q_len)):
+        _need(t, name, torch.int32, 1)
+    out = torch.empty_like(r)
+    rc = _lib("wkv").sb_wkv_scan(
+        _code(r.dtype), _ptr(r), _ptr(k), _ptr(v), _ptr(x_decay), _ptr(w0), _ptr(u), _ptr(g), _ptr(gain),
+        _ptr(state), ctypes.c_longlong(state.shape[1]), width, _ptr(h), width, _ptr(out), _ptr(seq_slot),
+        _ptr(seq_q_start), _ptr(seq_q_len), seq_slot.shape[0], heads, dim, ctypes.c_float(eps), _stream())
+    if rc == -2:
+        raise KernelError(f"the recurrence kernel takes heads of 1 to {wkv_max_dim()} channels, not {dim}")
+    _check(rc, "wkv_scan")
+    return out
+
+
+# ---------------------------------------------------------------------------------------- latent attention
+
+def latent_max_row() -> int:
+    return _lib("attention_latent").sb_latent_max_row()
+
+
+def latent_tables(rotation, rot_dims: int):
+    """``(cos, sin)`` for the latent-attention kernels: they turn the first ``rot_dims`` entries of the
+    rotated part in interleaved layout (entry ``2i`` with ``2i + 1``)."""
+    if rotation is None:
+        raise KernelError("latent attention needs a position part that offers a rotation")
+    if rotation.layout != "interleaved" or rotation.rotary_dim != rot_dims:
+        raise KernelError(f"the latent-attention kernels turn {rot_dims} entries in interleaved layout; asked for "
+                          f"{rotation.rotary_dim} in {rotation.layout!r} layout")
+    return rotation.cos, rotation.sin
+
+
+def latent_prepare(proj, q_gain, kv_gain, eps, cos_table, sin_table, tok_pos, tok_slot, block_table, store,
+                   q_rank, rank, rot, rot_dims, write_cache=True):
+    """What follows a token's stacked down-projections ``proj`` = ``[query latent | key/value latent | shared
+    key part]`` (the query latent alone with ``write_cache`` false): returns the RMS-normed query latent
+    ``[T, q_rank]``; norms the key/value latent, turns the shared key part by the token's position and files
+    both in the token's row of ``store`` ``[pages, 1, 64, rank + rot]``."""
+    _need(proj, "proj", None, 2)
+    n_tokens = proj.shape[0]
+    want = q_rank + (rank + rot if write_cache else 0)
+    if proj.shape[1] != want:
+        raise KernelError(f"proj has width {proj.shape[1]}, expected {want}")
+    _f32(q_gain, "query latent gain", (q_rank,))
+    _f32(cos_table, "cos_table")
+    _f32(sin_table, "sin_table")
+    if cos_table.dim() != 2 or cos_table.shape[1] < rot_dims // 2 or sin_table.shape != cos_table.shape:
+        raise KernelError("rotary tables must be [positions, at least rot_dims / 2]")
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    _need(tok_slot, "tok_slot", torch.int32, 1)
+    _need(block_table, "block_table", torch.int32, 2)
+    if write_cache:
+        _f32(kv_gain, "key/value latent gain", (rank,))
+        _need(store, "cache pages", proj.dtype, 4)
+        if tuple(store.shape[1:]) != (1, PAGE_TOKENS, rank + rot):
+            raise KernelError(f"cache pages have shape {tuple(store.shape)}, expected [pages, 1, {PAGE_TOKENS}, {rank + rot}]")
+    cq = torch.empty((n_tokens, q_rank), dtype=proj.dtype, device=proj.device)
+    rc = _lib("attention_latent").sb_latent_prepare(
+        _code(proj.dtype), _ptr(proj), proj.shape[1], _ptr(q_gain), _ptr(kv_gain if write_cache else None),
+        ctypes.c_float(eps), _ptr(cos_table), _ptr(sin_table), cos_table.shape[1], _ptr(tok_pos), _ptr(tok_slot),
+        _ptr(block_table), block_table.shape[1], _ptr(store if write_cache else None), _ptr(cq), n_tokens, q_rank,
+        rank, rot, rot_dims, int(write_cache), _stream())
+    _check(rc, "latent_prepare")
+    return cq
+
+
+def latent_rotate_q(q, qa, cos_table, sin_table, tok_pos, heads, dim, rot, rot_dims, rank):
+    """Turns the last ``rot`` entries of every head of ``q`` ``[T, heads * (dim + rot)]`` by the token's
+    position and files them behind the first ``rank`` entries of that head in ``qa`` ``[T, heads, rank + rot]``."""
+    _need(q, "q", None, 2)
+    _need(qa, "qa", q.dtype, 3)
+    if q.shape[1] != heads * (dim + rot) or tuple(qa.shape) != (q.shape[0], heads, rank + rot):
+        raise KernelError(f"q {tuple(q.shape)} / qa {tuple(qa.shape)} do not fit {heads} heads of {dim} + {rot}")
+    rc = _lib("attention_latent").sb_latent_rotate_q(
+        _code(q.dtype), _ptr(q), _ptr(qa), _ptr(cos_table), _ptr(sin_table), cos_table.shape[1], _ptr(tok_pos),
+        q.shape[0], heads, dim, rot, rot_dims, rank, _stream())
+    _check(rc, "latent_rotate_q")
+
+
+def latent_attention(qa, store, block_table, tok_slot, tok_pos, heads, rank, rot, scale, window=None):
+    """Softmax attention of every query row over its sequence's cached latent rows: ``qa`` ``[T, heads, rank
+    + rot]`` (queries with the key up-projection folded in, then the rotated part), ``store`` ``[pages, 1,
+    64, rank + rot]``; returns ``[T, heads, rank]``, the weighted sums of the latents."""
+    _need(qa, "qa", None, 3)
+    n_tokens = qa.shape[0]
+    if tuple(qa.shape[1:]) != (heads, rank + rot):
+        raise KernelError(f"qa has shape {tuple(qa.shape)}, expected [T, {heads}, {rank + rot}]")
+    if rank + rot > latent_max_row():
+        raise KernelError(f"latent rows of {rank + rot} entries exceed {latent_max_row()}")
+    _need(store, "cache pages", qa.dtype, 4)
+    if tuple(store.shape[1:]) != (1, PAGE_TOKENS, rank + rot):
+        raise KernelError(f"cache pages have shape {tuple(store.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    _need(tok_slot, "tok_slot", torch.int32, 1)
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    out = torch.empty((n_tokens, heads, rank), dtype=qa.dtype, device=qa.device)
+    rc = _lib("attention_latent").sb_latent_attention(
+        _code(qa.dtype), _ptr(qa), _ptr(out), _ptr(store), _ptr(block_table), block_table.shape[1], _ptr(tok_slot),
+        _ptr(tok_pos), n_tokens, heads, rank, rot, ctypes.c_float(scale), int(window or 0), _stream())
+    _check(rc, "latent_attention")
+    return out
+
+
+# ---------------------------------------------------------------------------------------- routed experts
+
+def moe_limits():
+    lib = _lib("moe")
+    return lib.sb_moe_max_experts(), lib.sb_moe_max_top()
+
+
+def moe_route(h, router, router_bias, top):
+    """``(ids int32 [T, top], weights float32 [T, top])``: the ``top`` largest of ``router @ h + bias``
+    (float32 ``[E, W]`` and ``[E]``), and the softmax over those alone."""
+    _need(h, "h", None, 2)
+    experts = router.shape[0]
+    _f32(router, "router", (experts, h.shape[1]))
+    if router_bias is not None:
+        _f32(router_bias, "router bias", (experts,))
+    ids = torch.empty((h.shape[0], top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((h.shape[0], top), dtype=torch.float32, device=h.device)
+    rc = _lib("moe").sb_moe_route(_code(h.dtype), _ptr(h), _ptr(router), _ptr(router_bias), _ptr(ids), _ptr(weights),
+                                  h.shape[0], h.shape[1], experts, top, _stream())
+    if rc == -2:
+        raise KernelError(f"the router takes up to {moe_limits()[0]} experts and {moe_limits()[1]} choices, not "
+                          f"{experts} and {top}")
+    _check(rc, "moe_route")
+    return ids, weights
+
+
+def moe_experts(h, ids, weights, gate_up, down, limit):
+    """The chosen experts of every row and their weighted sum: ``gate_up`` ``[E, 2 * F, W]`` (an expert's
+    gate rows, then its up rows), ``down`` ``[E, W, F]``; an expert is ``down(g * sigmoid(1.702 g) * (u +
+    1))`` with ``g = min(gate(h), limit)`` and ``u = clamp(up(h), -limit, limit)``.  Returns ``[T, W]``."""
+    _need(h, "h", None, 2)
+    _need(gate_up, "gate_up", h.dtype, 3)
+    _need(down, "down", h.dtype, 3)
+    _need(ids, "ids", torch.int32, 2)
+    _need(weights, "weights", torch.float32, 2)
+    n_tokens, width = h.shape
+    experts, two_f, _ = gate_up.shape
+    inner = two_f // 2
+    top = ids.shape[1]
+    if tuple(gate_up.shape) != (experts, 2 * inner, width) or tuple(down.shape) != (experts, width, inner):
+        raise KernelError(f"expert weights {tuple(gate_up.shape)} / {tuple(down.shape)} do not fit rows of {width}")
+    lib = _lib("moe")
+    bm = lib.sb_moe_tile_rows()
+    n_pairs = n_tokens * top
+    max_tiles = -(-n_pairs // bm) + min(experts, n_pairs)
+    capacity = max_tiles * bm
+    meta = torch.empty((capacity + max_tiles + 1,), dtype=torch.int32, device=h.device)
+    sorted_pairs, tile_expert, n_tiles = meta[:capacity], meta[capacity:capacity + max_tiles], meta[capacity + max_tiles:]
+    rc = lib.sb_moe_align(_ptr(ids), n_pairs, experts, _ptr(sorted_pairs), capacity, _ptr(tile_expert), _ptr(n_tiles),
+                          _stream())
+    _check(rc, "moe_align")
+    act = torch.empty((capacity, inner), dtype=h.dtype, device=h.device)
+    rc = lib.sb_moe_tiles(_code(h.dtype), 1, _ptr(h), _ptr(gate_up), _ptr(act), _ptr(sorted_pairs), _ptr(tile_expert),
+                          _ptr(n_tiles), max_tiles, width, inner, top, ctypes.c_float(limit), _stream())
+    _check(rc, "moe_up")
+    per_pair = torch.empty((n_pairs, width), dtype=h.dtype, device=h.device)
+    rc = lib.sb_moe_tiles(_code(h.dtype), 0, _ptr(act), _ptr(down), _ptr(per_pair), _ptr(sorted_pairs),
+                          _ptr(tile_expert), _ptr(n_tiles), max_tiles, inner, width, top, ctypes.c_float(limit), _stream())
+    _check(rc, "moe_down")
+    out = torch.empty_like(h)
+    rc = lib.sb_moe_combine(_code(h.dtype), _ptr(per_pair), _ptr(weights), _ptr(out), n_tokens, width, top, _stream())
+    _check(rc, "moe_combine")
+    return out

@@ -43,6 +43,9 @@ ROLES = {
     "slope": Role(0.5, 0.1, always_32bit=True),          # the scalar inside a Dynamic Tanh
     "vector32": Role(0.0, 0.1, always_32bit=True),       # small learnt vectors (lambda's factors)
     "stream_weight": Role(0.25, 0.2, always_32bit=True),  # how streams are read, written and mixed
+    "gain_offset": Role(0.0, 0.1, always_32bit=True),    # a norm's gain stored around zero (gain - 1)
+    "shift": Role(0.5, 0.2, always_32bit=True),          # how much of the previous token a mix takes
+    "matrix32": Role(0.0, 0.02, always_32bit=True),      # a small projection computed in 32-bit (a router)
 }
 
 

@@ -36,3 +36,74 @@ class GatedFeedForward(Part):
 
     def weight_bytes(self):
         return bytes_of(self.gate_up, self.down)
+
+
+class BiasedFeedForward(Part):
+    """``down(act(up(x) + b_up)) + b_down`` with the activation of the spec (``relu2``: the square of relu).
+    The down bias can be left to whoever writes the output to the residual stream (``defer_bias``)."""
+
+    can_defer_bias = True
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        if spec.activation not in ops.BIAS_ACTIVATIONS:
+            raise ValueError(f"the biased feed-forward implements relu2 and tanh, not {spec.activation!r}")
+        self.deferred_bias = None
+
+    def param_specs(self):
+        h, i = self.spec.hidden_size, self.spec.intermediate_size
+        return {"up": ParamSpec((i, h)), "up_bias": ParamSpec((i,), "bias32"),
+                "down": ParamSpec((h, i)), "down_bias": ParamSpec((h,), "bias32")}
+
+    def set_params(self, params):
+        self.up, self.down = params["up"].contiguous(), params["down"].contiguous()
+        self.up_bias = params["up_bias"].float().contiguous()
+        self.deferred_bias = params["down_bias"].float().contiguous()
+
+    def __call__(self, x, ctx=None, defer_bias=False):
+        status = ctx.status if ctx is not None else None
+        act = ops.bias_act(ops.linear(x, self.up, status=status), self.up_bias, self.spec.activation)
+        y = ops.linear(act, self.down, status=status)
+        return y if defer_bias else ops.bias_act(y, self.deferred_bias, None)
+
+    def weight_bytes(self):
+        return bytes_of(self.up, self.up_bias, self.down, self.deferred_bias)
+
+
+class RoutedExperts(Part):
+    """A mixture of small gated experts: the router's logits in 32-bit, the ``top`` largest, softmax over
+    those; the chosen experts of all tokens run as tiles grouped by expert (``ops.moe_experts``), without a
+    word from the host, so the part also runs inside a captured step."""
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        if spec.top > spec.experts:
+            raise ValueError(f"{spec.top} choices among {spec.experts} experts")
+
+    def param_specs(self):
+        s = self.spec
+        out = {"router": ParamSpec((s.experts, s.hidden_size), "matrix32"),
+               "router_bias": ParamSpec((s.experts,), "bias32")}
+        for e in range(s.experts):
+            out[f"e{e}_gate"] = ParamSpec((s.intermediate_size, s.hidden_size))
+            out[f"e{e}_up"] = ParamSpec((s.intermediate_size, s.hidden_size))
+            out[f"e{e}_down"] = ParamSpec((s.hidden_size, s.intermediate_size))
+        return out
+
+    def set_params(self, params):
+        s = self.spec
+        self.router = params["router"].float().contiguous()
+        self.router_bias = params["router_bias"].float().contiguous()
+        self.gate_up = torch.stack([torch.cat([params[f"e{e}_gate"], params[f"e{e}_up"]], dim=0)
+                                    for e in range(s.experts)]).contiguous()
+        self.down = torch.stack([params[f"e{e}_down"] for e in range(s.experts)]).contiguous()
+
+    def __call__(self, x, ctx=None):
+        s = self.spec
+        ids, weights = ops.moe_route(x, self.router, self.router_bias, s.top)
+        return ops.moe_experts(x, ids, weights, self.gate_up, self.down, s.limit)
+
+    def weight_bytes(self):
+        """What a step reads at most: the router and every expert (a step of few tokens reads only the
+        experts they choose)."""
+        return bytes_of(self.router, self.router_bias, self.gate_up, self.down)

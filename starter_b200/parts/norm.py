@@ -11,10 +11,15 @@ class RMSNorm(Part):
     (engine/engine.py:75-88, engine/kernels/rmsnorm.py:21-45)."""
 
     def param_specs(self):
+        if getattr(self.spec, "unit_offset", False):
+            return {"weight": ParamSpec((self.spec.size,), "gain_offset")}
         return {"weight": ParamSpec((self.spec.size,), "gain")}
 
     def set_params(self, params):
         self.weight = params["weight"]
+        if getattr(self.spec, "unit_offset", False):
+            # stored around zero: the gain is formed once, in float32, and the kernels see a plain gain
+            self.weight = (1.0 + self.weight.float()).contiguous()
 
     def __call__(self, x):
         return ops.rmsnorm(x, self.weight, self.spec.eps)

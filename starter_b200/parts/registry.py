@@ -25,12 +25,15 @@ from __future__ import annotations
 
 from .attention import GroupedQueryAttention
 from .attention_diff import DifferentialAttention
+from .attention_latent import LatentAttention
 from .block import PreNormBlock
-from .feedforward import GatedFeedForward
+from .feedforward import BiasedFeedForward, GatedFeedForward, RoutedExperts
 from .hyper import HyperConnection, HyperMixerOnlyBlock, HyperPreNormBlock
 from .norm import RMSNorm
 from .norm_dyt import DynamicTanh
-from .rotary import RotaryTable
+from .rotary import InterleavedRotaryTable, RotaryTable
+from .sandwich import SandwichBlock, SandwichMixerOnlyBlock
+from .wkv import WkvMixer
 
 FAMILIES = ("mixer", "feed_forward", "norm", "position", "connection", "arrangement")
 _REGISTRY = {family: {} for family in FAMILIES}
@@ -60,3 +63,10 @@ register("norm", "dynamic_tanh", DynamicTanh)
 register("connection", "hyper", HyperConnection)
 register("arrangement", "hyper_prenorm", HyperPreNormBlock)
 register("arrangement", "hyper_mixer_only", HyperMixerOnlyBlock)
+register("mixer", "latent_attention", LatentAttention)
+register("mixer", "wkv", WkvMixer)
+register("feed_forward", "dense_biased", BiasedFeedForward)
+register("feed_forward", "routed_experts", RoutedExperts)
+register("position", "rope_interleaved", InterleavedRotaryTable)
+register("arrangement", "sandwich", SandwichBlock)
+register("arrangement", "sandwich_mixer_only", SandwichMixerOnlyBlock)

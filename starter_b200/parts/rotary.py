@@ -65,3 +65,27 @@ class RotaryTable(Part):
         self.sin = freqs.sin().contiguous().to(self.device)
         self.length = size
         return True
+
+
+class InterleavedRotaryTable(RotaryTable):
+    """Tables for a rotation of entry ``2i`` with entry ``2i + 1`` over the first ``dims`` entries of a
+    vector: ``[positions, dims / 2]`` of ``cos`` and ``sin`` of ``position * base ** (-2i / dims)``.  The
+    angles are formed in float64 on the host and the tables rounded to float32 once."""
+
+    def rotation(self) -> Rotation:
+        return Rotation(self.cos, self.sin, self.spec.dims, "interleaved")
+
+    def ensure(self, length: int) -> bool:
+        if length <= self.length:
+            return False
+        size = max(self.MIN_POSITIONS, self.length)
+        while size < length:
+            size *= 2
+        dims = self.spec.dims
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        freq = torch.pow(torch.tensor(float(self.spec.base), dtype=torch.float64), -2.0 * i / dims)
+        angles = torch.outer(torch.arange(size, dtype=torch.float64), freq)
+        self.cos = angles.cos().float().contiguous().to(self.device)
+        self.sin = angles.sin().float().contiguous().to(self.device)
+        self.length = size
+        return True
