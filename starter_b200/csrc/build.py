@@ -49,6 +49,10 @@ SOURCES = (
     "attention_diff",
     "attention_diff_prefill",
     "attention_diff_prefill_tc",
+    "residual32",
+    "wkv",
+    "attention_latent",
+    "moe",
 )
 
 _lock = threading.Lock()

@@ -49,7 +49,7 @@ __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restr
 // Thread (j, p) holds S[i][j] for i = p, p + P, ...: KPT values.  P is a power of two (at most 32),
 // the P threads of a j are neighbouring lanes and sum their parts of o[j] by shuffles.
 template <typename T, int KPT>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(KPT > 32 ? 1024 : 512)
 wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                 const float* __restrict__ x_decay, const float* __restrict__ w0, const float* __restrict__ u,
                 const T* __restrict__ g, const float* __restrict__ gain, float* __restrict__ state,
@@ -180,16 +180,24 @@ static int launch_scan(const void* r, const void* k, const void* v, const float*
                        int state_offset, const void* h, int width, void* out, const int* seq_slot,
                        const int* seq_q_start, const int* seq_q_len, int n_seqs, int heads, int D, float eps,
                        cudaStream_t s) {
-  const int kpt = D <= 64 ? 8 : 32;
+  const int kpt = D <= 64 ? 8 : D <= 128 ? 32 : 64;
   int P = 1;
   while (P * kpt < D) P *= 2;
   int threads = (D * P + 31) / 32 * 32;
-  if (P > 32 || threads > 512 || 4 * WKV_CHUNK * D > WKV_PREFETCH * threads) return -2;
+  if (P > 32 || threads > (kpt > 32 ? 1024 : 512) || 4 * WKV_CHUNK * D > WKV_PREFETCH * threads) return -2;
   const size_t smem = (size_t)(2 * 4 + 1) * WKV_CHUNK * D * sizeof(float);
   const dim3 grid(n_seqs, heads);
   if (kpt == 8) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(wkv_scan_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_dependent(wkv_scan_kernel<T, 8>, grid, dim3(threads), smem, s, (const T*)r, (const T*)k, (const T*)v,
+                            x_decay, w0, u, (const T*)g, gain, state, state_stride, state_offset, (const T*)h, width,
+                            (T*)out, seq_slot, seq_q_start, seq_q_len, heads, D, P, eps);
+  }
+  if (kpt == 64) {
+    // heads of up to 256 channels: 64 state values a thread at 1,024 threads, which the compiler keeps
+    // partly in local memory; correct, and slower than the sizes above
+    cudaFuncSetAttribute(wkv_scan_kernel<T, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_dependent(wkv_scan_kernel<T, 64>, grid, dim3(threads), smem, s, (const T*)r, (const T*)k, (const T*)v,
                             x_decay, w0, u, (const T*)g, gain, state, state_stride, state_offset, (const T*)h, width,
                             (T*)out, seq_slot, seq_q_start, seq_q_len, heads, D, P, eps);
   }
@@ -201,7 +209,7 @@ static int launch_scan(const void* r, const void* k, const void* v, const float*
 
 extern "C" {
 
-int sb_wkv_max_dim() { return 128; }
+int sb_wkv_max_dim() { return 256; }
 
 // h: [n_tokens, width]; state: float [slots, state_stride], a slot's first `width` floats hold the
 // mixer input of the last token before this step; mu: float [n_mix, width]; out: [n_mix, n_tokens, width].
@@ -224,7 +232,7 @@ int sb_wkv_scan(int dtype, const void* r, const void* k, const void* v, const fl
                 int state_offset, const void* h, int width, void* out, const int* seq_slot, const int* seq_q_start,
                 const int* seq_q_len, int n_seqs, int heads, int dim, float eps, cudaStream_t s) {
   if (n_seqs == 0) return 0;
-  if (dim < 1 || dim > 128 || heads < 1) return -2;
+  if (dim < 1 || dim > 256 || heads < 1) return -2;
   if (dtype == 0)
     return launch_scan<float>(r, k, v, x_decay, w0, u, g, gain, state, (size_t)state_stride, state_offset, h, width,
                               out, seq_slot, seq_q_start, seq_q_len, n_seqs, heads, dim, eps, s);

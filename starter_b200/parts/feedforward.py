@@ -79,6 +79,9 @@ class RoutedExperts(Part):
         super().__init__(spec, dtype)
         if spec.top > spec.experts:
             raise ValueError(f"{spec.top} choices among {spec.experts} experts")
+        #: the experts chosen in the latest call (int32 ``[T, top]``, on the device), for whoever wants to
+        #: look at the routing
+        self.last_ids = None
 
     def param_specs(self):
         s = self.spec
@@ -101,6 +104,7 @@ class RoutedExperts(Part):
     def __call__(self, x, ctx=None):
         s = self.spec
         ids, weights = ops.moe_route(x, self.router, self.router_bias, s.top)
+        self.last_ids = ids
         return ops.moe_experts(x, ids, weights, self.gate_up, self.down, s.limit)
 
     def weight_bytes(self):

@@ -159,8 +159,14 @@ def route(h, w, p, top):
     return best.indices, torch.softmax(best.values, dim=-1)
 
 
-def routed_feed_forward(h, w, p, mlp):
+def routed_feed_forward(h, w, p, mlp, chosen=None):
+    """``chosen`` (``[T, top]``): use these experts instead of the largest logits (their weights are still
+    the softmax over their own logits); for comparisons in which a near-tie may fall either way."""
     index, weight = route(h, w, p, mlp["router"]["top"])
+    if chosen is not None:
+        z = h @ w[p + "router"].T + w[p + "router.b"]
+        index = torch.as_tensor(chosen).long()
+        weight = torch.softmax(z.gather(1, index), dim=-1)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(index[t].tolist(), weight[t]):
@@ -170,9 +176,9 @@ def routed_feed_forward(h, w, p, mlp):
 
 # ------------------------------------------------------------------------------------------ the model
 
-def forward(cfg, w, tokens, layers_out=None):
+def forward(cfg, w, tokens, layers_out=None, routes=None):
     """Logits ``[T, vocab]`` of one sequence from its first token; ``layers_out`` (a list) receives the
-    residual stream after every layer."""
+    residual stream after every layer; ``routes`` ({layer: ``[T, top]``}) fixes the experts of routed layers."""
     eps = cfg["norm"]["eps"]
     T = len(tokens)
     positions = torch.arange(T)
@@ -199,8 +205,18 @@ def forward(cfg, w, tokens, layers_out=None):
             if mlp["kind"] == "dense":
                 y = dense_feed_forward(h, w, p + "mlp.")
             else:
-                y = routed_feed_forward(h, w, p + "mlp.", mlp)
+                y = routed_feed_forward(h, w, p + "mlp.", mlp, None if routes is None else routes.get(i))
             x = x + norm_around_zero(y, w[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
     return norm_around_zero(x, w["final.norm"], eps) @ w["head"].T
+
+
+def generate(cfg, w, prompt, n):
+    """Greedy continuation: ``n`` tokens, each the largest logit (the lowest index among equals)."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        tok = int(torch.argmax(forward(cfg, w, seq)[-1]))
+        out.append(tok)
+        seq.append(tok)
+    return out
