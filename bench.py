@@ -504,6 +504,254 @@ def design_compare(args) -> int:
     return 0
 
 
+def kesedra_config(size: dict, layers: int) -> dict:
+    """Kesedra at ``size``: of every four layers a recurrent one with a dense feed-forward, latent attention
+    with routed experts, a recurrent one with routed experts, and latent attention over the second layer's
+    latent with a dense feed-forward.  Recurrent heads of 64 channels; latent attention with 128 plain + 64
+    rotated query/key entries and values of 128 a head over a latent of 512, a window of 1,024; 16 experts of a
+    quarter of the dense width, four a token (as many active feed-forward rows as the dense layer)."""
+    w, out = size["width"], []
+    moe = dict(kind="moe", expert=dict(ff=size["ff"] // 4 // 64 * 64, limit=7.0), router=dict(experts=16, top=4))
+    dense = dict(kind="dense", ff=size["ff"])
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer, kind = dict(heads=w // 64, dim=64, decay_rank=64), "wkv"
+        else:
+            mixer, kind = dict(heads=size["heads"], dim=128, rot_dim=64, vdim=128, q_rank=w * 3 // 4 // 64 * 64, kv_rank=512,
+                               scale=192 ** -0.5, mask=dict(size=1024), rot=dict(base=10000.0, dims=64)), "latent_attention"
+            if i % 4 == 3:
+                mixer["kv_from"] = i - 2
+        out.append(dict(type=kind, mixer=mixer, mlp=dense if i % 4 in (0, 3) else moe))
+    return dict(architecture="Kesedra", vocab=size["vocab"], width=w, embedding=dict(scale=16.0), norm=dict(eps=1e-5),
+                layers=out)
+
+
+def kesedra_compare(args) -> int:
+    """``--design kesedra``: prefill and decode throughput of Kesedra beside Qwen3 (the closest model this
+    library has) at equal width, dense feed-forward, vocabulary and head count, and Kesedra's own kernels
+    alone beside Qwen3's like kernels, each against its roofline.  Every number is timed on the device with
+    CUDA events; the kernels alone run inside a CUDA graph, once per layer.  Prints one JSON line."""
+    import torch
+
+    from starter_b200 import ops
+    from starter_b200.config import config_from_dict
+    from starter_b200.engine import ModelRunner, StepEntry, random_model
+
+    pk = peaks()
+    layers = args.layers if args.layers_given else 8
+    batch, context, prompt_len = args.batch, 2048, PROMPT
+    warmup, steps = max(args.warmup, 3), max(min(args.steps, 64), 1)
+    sampler = ClockSampler()
+    sampler.start()
+    windows = []
+    gen = torch.Generator().manual_seed(0)
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+
+    def timed(fn, reps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.monotonic()
+        start.record()
+        for _ in range(reps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        windows.append((t0, time.monotonic()))
+        return start.elapsed_time(stop) / reps
+
+    def in_graph(calls):
+        """Microseconds per call of ``calls`` (one per layer), captured together and replayed."""
+        for c in calls:
+            c()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for c in calls:
+                c()
+        graph.replay()
+        return timed(graph.replay, 5) / len(calls) * 1e3
+
+    def rnd(*shape):
+        return (torch.randn(*shape, device=dev) * 0.5).to(bf)
+
+    def bw(us, moved):
+        return dict(us=us, gbs=moved / us / 1e3, frac_of_copy_peak=moved / us / 1e3 / pk["hbm_gbs"])
+
+    def tc(us, flops):
+        return dict(us=us, tflops=flops / us / 1e6, frac_of_bf16_peak=flops / us / 1e6 / pk["bf16_tflops"])
+
+    def kernels_alone(model, runner, design, size):
+        spec = model.spec
+        blocks = [model.blocks[e.layer] for e in spec.schedule]
+        cache = runner.cache
+        w = size["width"]
+        out = {}
+        slots = [runner.open_sequence() for _ in range(batch)]
+        for s in slots:
+            runner.step([StepEntry(s, torch.randint(0, spec.vocab_size, (context,), generator=gen).tolist(), [])])
+        for rows, name in ((prompt_len, "prompt"), (batch, "decode")):
+            if rows == prompt_len:
+                slot = runner.open_sequence()
+                ctx = runner.make_context([StepEntry(slot, [1] * prompt_len, [])])
+            else:
+                ctx = runner.make_context([StepEntry(s, [1], []) for s in slots])
+            x = rnd(rows, w)
+            if design == "kesedra":
+                res = torch.randn(rows, w, device=dev)
+                us = in_graph([lambda b=b: ops.residual_norm(res, bf, 1e-5, (x, b.norm1b.weight, None, 1e-5), b.norm2.weight)
+                               for b in blocks])
+                out[f"{name}: post-norm + residual sum + norm"] = bw(us, rows * w * (2 + 4 + 4 + 2))
+                rec = [(b, e.cache) for b, e in zip(blocks, spec.schedule) if b.mixer.spec.kind == "wkv"]
+                m = rec[0][0].mixer
+                hd, heads, dim = m.inner, m.spec.num_heads, m.spec.head_dim
+                r, k, v, g = (rnd(rows, hd) for _ in range(4))
+                xd = torch.rand(rows, hd, device=dev)
+                us = in_graph([lambda b=b, e=e: ops.token_shift(x, cache.entry_state(e), b.mixer.mu, ctx.tok_slot) for b, e in rec])
+                out[f"{name}: token shift (five mixes)"] = bw(us, rows * w * 2 * 6)
+                us = in_graph([lambda b=b, e=e: ops.wkv_scan(r, k, v, xd, b.mixer.u, g, b.mixer.gain, cache.entry_state(e),
+                                                              x, ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len, heads, dim, 1e-5)
+                               for b, e in rec])
+                state_bytes = ctx.n_seqs * heads * dim * dim * 4 * 2
+                d = bw(us, rows * hd * (5 * 2 + 4) + state_bytes)
+                d["gflops"] = rows * heads * dim * dim * 6 / us / 1e3
+                out[f"{name}: recurrence (state walk, head norm, gate)"] = d
+                att = [(b, e.cache, e.writes_cache) for b, e in zip(blocks, spec.schedule) if b.mixer.spec.kind == "latent_attention"]
+                m = att[0][0].mixer
+                sp = m.spec
+                proj = rnd(rows, m.down.shape[0])
+                cos, sin = ops.latent_tables(m.position.rotation(), sp.position.dims)
+                own = [(b, e) for b, e, wr in att if wr]
+                us = in_graph([lambda b=b, e=e: ops.latent_prepare(proj, b.mixer.q_gain, b.mixer.kv_gain, 1e-5, cos, sin, ctx.tok_pos,
+                                                                    ctx.tok_slot, cache.block_table, cache.entry_pages(e)[0], sp.q_rank,
+                                                                    sp.kv_rank, sp.rot_dim, sp.position.dims) for b, e in own])
+                out[f"{name}: latent norms, rotation, cache write"] = bw(us, rows * 2 * (proj.shape[1] + sp.q_rank + m.row))
+                qa = rnd(rows, sp.num_heads, m.row)
+                us = in_graph([lambda b=b, e=e: ops.latent_attention_step(qa, cache.entry_pages(e)[0], cache.block_table, ctx,
+                                                                           sp.num_heads, sp.kv_rank, sp.rot_dim, sp.scale, sp.window)
+                               for b, e in own])
+                if rows == prompt_len:
+                    seen = sum(min(p + 1, sp.window) for p in range(prompt_len))
+                    out[f"{name}: attention"] = tc(us, sp.num_heads * 2 * (m.row + sp.kv_rank) * seen)
+                else:
+                    out[f"{name}: attention"] = bw(us, batch * min(context + 1, sp.window) * m.row * 2)
+                routed = [b for b in blocks if getattr(b.feed_forward, "last_ids", "no") != "no"]
+                ff = routed[0].feed_forward
+                fs = ff.spec
+                ids, weights = ops.moe_route(x, ff.router, ff.router_bias, fs.top)
+                us = in_graph([lambda b=b: ops.moe_route(x, b.feed_forward.router, b.feed_forward.router_bias, fs.top) for b in routed])
+                out[f"{name}: router"] = bw(us, rows * w * 2 + fs.experts * w * 4)
+                us = in_graph([lambda b=b: ops.moe_experts(x, ids, weights, b.feed_forward.gate_up, b.feed_forward.down, fs.limit)
+                               for b in routed])
+                flops = rows * fs.top * 3 * fs.intermediate_size * w * 2
+                if rows == prompt_len:
+                    out[f"{name}: experts (gate, up, down, sum)"] = tc(us, flops)
+                else:
+                    used = min(fs.experts, rows * fs.top)
+                    out[f"{name}: experts (gate, up, down, sum)"] = bw(us, used * 3 * fs.intermediate_size * w * 2)
+            else:
+                heads, kvh = size["heads"], size["kv_heads"]
+                res = x.clone()
+                us = in_graph([lambda b=b: ops.rmsnorm(res, b.norm1.weight, b.norm1.spec.eps, delta=x) for b in blocks])
+                out[f"{name}: residual sum + norm"] = bw(us, rows * w * 2 * 4)
+                m = blocks[0].mixer
+                sp = m.spec
+                qkv = rnd(rows, m.qkv.shape[0])
+                rot = m.position.rotation()
+                entries = [(b, e.cache) for b, e in zip(blocks, spec.schedule)]
+
+                def store(b, e):
+                    k, v = cache.entry_pages(e)
+                    return ops.qk_norm_rope_store(qkv, heads, kvh, sp.head_dim, b.mixer.q_norm, b.mixer.k_norm, sp.qk_norm_eps,
+                                                  rot.cos, rot.sin, ctx.tok_pos, ctx.tok_slot, cache.block_table, k, v)
+
+                def attend(b, e):
+                    k, v = cache.entry_pages(e)
+                    if rows == batch:
+                        return ops.attention_decode_qkv(qkv, k, v, cache.block_table, ctx.seq_slot, ctx.seq_kv_len, heads, kvh,
+                                                        sp.head_dim, sp.scale, None, b.mixer.q_norm, b.mixer.k_norm,
+                                                        sp.qk_norm_eps, rot.cos, rot.sin, write_cache=True, kv_hint=ctx.max_kv_len)
+                    return ops.attention_prefill(store(b, e), k, v, cache.block_table, ctx.seq_slot, ctx.seq_q_start,
+                                                 ctx.seq_q_len, ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first, heads, kvh,
+                                                 sp.head_dim, sp.scale, None, max_q_len=ctx.max_q_len,
+                                                 blocks=(ctx.block_seq, ctx.block_first))
+
+                us = in_graph([lambda b=b, e=e: attend(b, e) for b, e in entries])
+                if rows == prompt_len:
+                    us_store = in_graph([lambda b=b, e=e: store(b, e) for b, e in entries])
+                    out[f"{name}: head norm, rotation, cache write"] = bw(us_store, rows * 2 * (qkv.shape[1] + (heads + 2 * kvh) * sp.head_dim))
+                    out[f"{name}: attention"] = tc(us - us_store, heads * 4 * sp.head_dim * prompt_len * (prompt_len + 1) / 2)
+                else:
+                    out[f"{name}: attention"] = bw(us, batch * (context + 1) * 2 * kvh * sp.head_dim * 2)
+                ff = blocks[0].feed_forward
+                us = in_graph([lambda b=b: b.feed_forward(x, None) for b in blocks])
+                flops = rows * 3 * ff.spec.intermediate_size * w * 2
+                if rows == prompt_len:
+                    out[f"{name}: feed-forward (gate, up, down)"] = tc(us, flops)
+                else:
+                    out[f"{name}: feed-forward (gate, up, down)"] = bw(us, 3 * ff.spec.intermediate_size * w * 2)
+            if rows == prompt_len:
+                runner.close_sequence(slot)
+            else:
+                for slot_, length in zip(ctx.host["seq_slot"].tolist(), ctx.host["seq_kv_len"].tolist()):
+                    cache.lengths[slot_] = length - 1       # the context made above counted a token that no step ran
+        for s in slots:
+            runner.close_sequence(s)
+        return {k: {a: round(b, 4 if "frac" in a else 1) for a, b in v.items()} for k, v in out.items()}
+
+    results = {}
+    for size_name in (args.design_sizes.split(",") if args.design_sizes else list(DESIGN_SIZES)):
+        size = DESIGN_SIZES[size_name]
+        row = {"layers": layers}
+        for design, raw in (("kesedra", kesedra_config(size, layers)), ("qwen3", qwen3_config(size, layers))):
+            config = config_from_dict(raw)
+            model = random_model(config, seed=0, dtype="bfloat16")
+            vocab = model.spec.vocab_size
+            runner = ModelRunner(model, max_tokens=(batch + 1) * (context + 256) + prompt_len, max_sequences=batch + 2)
+            prompt = torch.randint(0, vocab, (prompt_len,), generator=gen).tolist()
+
+            def prefill_once():
+                slot = runner.open_sequence()
+                runner.step([StepEntry(slot, prompt, [prompt_len - 1])])
+                runner.close_sequence(slot)
+
+            for _ in range(warmup):
+                prefill_once()
+            prefill_ms = timed(prefill_once, 5)
+            slots = [runner.open_sequence() for _ in range(batch)]
+            for s in slots:
+                runner.reserve(s, context + 256)
+                runner.step([StepEntry(s, torch.randint(0, vocab, (context,), generator=gen).tolist(), [])])
+            entries = [StepEntry(s, [1], [0]) for s in slots]
+
+            def one():
+                runner.decode_tokens(entries, [0.0] * batch, [0] * batch)
+
+            for _ in range(warmup):
+                one()
+            decode_ms = timed(one, steps)
+            for s in slots:
+                runner.close_sequence(s)
+            runner.check_status()
+            row[design] = {
+                "prefill_tok_s": round(prompt_len / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+                "decode_tok_s": round(batch / decode_ms * 1e3, 1), "decode_ms_per_step": round(decode_ms, 4),
+                "weight_mb_per_step": round(model.step_weight_bytes() / 1e6, 1),
+                "kernels_per_decode_step": runner.graphs.kernels_per_replay.get(batch),
+                "kernels": kernels_alone(model, runner, design, size),
+            }
+            del runner, model
+            torch.cuda.empty_cache()
+        results[size_name] = row
+    print(json.dumps({
+        "metric": "prefill tok/s at 2,048 tokens and decode tok/s at batch %d, context 2,048: Kesedra beside Qwen3 at "
+                  "equal sizes (BF16, random weights)" % batch,
+        "unit": "tok/s", "n_gpus": 1, "dtype": "bf16", "steps": steps, "warmup": warmup,
+        "data": "synthetic: random weights, uniform random token ids", "peaks": pk,
+        "sizes": {k: DESIGN_SIZES[k] for k in results}, "results": results, "clocks": sampler.stop(windows)}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -521,7 +769,7 @@ def main() -> int:
                              "generation range); the cache is sized for it")
     parser.add_argument("--per-stage", action="store_true",
                         help="also print where a decode step's time goes, kernel by kernel (stderr)")
-    parser.add_argument("--design", choices=["goguvik"], default=None,
+    parser.add_argument("--design", choices=["goguvik", "kesedra"], default=None,
                         help="instead of the default run: that design beside Qwen3 at equal sizes (prefill, decode, "
                              "and each design's own kernels against their rooflines)")
     parser.add_argument("--design-sizes", default=None, help="comma-separated subset of " + ",".join(DESIGN_SIZES))
@@ -534,6 +782,8 @@ def main() -> int:
         return reference_arm(args)
     if args.workload:
         return workload(args)
+    if args.design == "kesedra":
+        return kesedra_compare(args)
     if args.design:
         return design_compare(args)
     warmup = max(args.warmup, 3)

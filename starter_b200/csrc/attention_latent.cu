@@ -245,3 +245,308 @@ int sb_latent_attention(int dtype, const void* qa, void* out, const void* store,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------- tensor cores
+// The same attention for bfloat16 on mma.sync tiles (rank and rot multiples of 16).  A block owns up to
+// 64 query rows: the heads (up to 64 of them) of consecutive tokens of one sequence, which all score the
+// same cache rows.  It walks the keys its tokens can see in blocks of 32 (a block of keys never leaves a
+// page), double-buffered by cp.async; eight warps = four groups of 16 query rows times two halves of the
+// value columns.  Both halves form the same scores S = Q K^T (16 x 32 a warp, float), mask them by each
+// row's own position and window, keep the running maximum and sum per row, and add P V for their half of
+// the latent's columns, V being the first `rank` entries of the very key rows in shared memory.
+// With n_splits > 1 the key blocks are dealt out to gridDim.y blocks, which leave (maximum, sum,
+// unnormalised sums) per row in scratch memory for latent_merge_kernel: single tokens of few sequences.
+#define LA_BM 64
+#define LA_BN 32
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool real) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int bytes = real ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm4(unsigned (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm4_t(unsigned (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&p);
+}
+
+template <int NT>   // 8-column tiles of the latent a warp sums (its half of the value columns, rounded up)
+__global__ void __launch_bounds__(256, 1)
+latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, float* __restrict__ part_acc,
+                           float* __restrict__ part_ml, const bf16* __restrict__ store,
+                           const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slot,
+                           const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                           const int* __restrict__ seq_kv_len, const int* __restrict__ tile_seq,
+                           const int* __restrict__ tile_first, int heads, int rank, int rot, float scale, int window,
+                           int tokens_per_block, int heads_per_block, int head_chunks, int subs, int n_rows_total) {
+  extern __shared__ __align__(16) unsigned char latent_smem[];
+  const int Dk = rank + rot, ld = Dk + 8;
+  bf16* qs = reinterpret_cast<bf16*>(latent_smem);
+  bf16* ks = qs + LA_BM * ld;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int per_tile = subs * head_chunks;
+  const int tile = blockIdx.x / per_tile, rem = blockIdx.x % per_tile;
+  const int sub = rem / head_chunks, hc = rem % head_chunks;
+  const int split = blockIdx.y, n_splits = gridDim.y;
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(qa); SB_BEHIND_WAIT(store); SB_BEHIND_WAIT(block_table);
+  SB_BEHIND_WAIT(seq_slot); SB_BEHIND_WAIT(seq_q_start); SB_BEHIND_WAIT(seq_q_len); SB_BEHIND_WAIT(seq_kv_len);
+  SB_BEHIND_WAIT(tile_seq); SB_BEHIND_WAIT(tile_first);
+  const int seq = tile_seq[tile];
+  const int q_len = seq_q_len[seq];
+  const int first_tok = tile_first[tile] + sub * tokens_per_block;
+  if (sub * tokens_per_block >= 64 || first_tok >= q_len) return;
+  int n_tok = min(tokens_per_block, q_len - first_tok);
+  n_tok = min(n_tok, 64 - sub * tokens_per_block);
+  const int h0 = hc * heads_per_block;
+  const int n_heads = min(heads_per_block, heads - h0);
+  const int kv_len = seq_kv_len[seq], q_start = seq_q_start[seq];
+  const int* pages = block_table + (size_t)seq_slot[seq] * table_stride;
+  const int p_first = kv_len - q_len + first_tok, p_last = p_first + n_tok - 1;
+  const int j_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int b_lo = j_lo / LA_BN, n_blocks = p_last / LA_BN - b_lo + 1;
+  const int per_split = (n_blocks + n_splits - 1) / n_splits;
+  const int b_begin = b_lo + split * per_split, b_end = min(b_lo + n_blocks, b_begin + per_split);
+  const int chunks = Dk / 8;                      // 16-byte pieces of a row
+
+  auto load_keys = [&](int b, int buf) {
+    bf16* dst = ks + (size_t)buf * LA_BN * ld;
+    for (int i = tid; i < LA_BN * chunks; i += 256) {
+      const int kr = i / chunks, c = i - kr * chunks;
+      const int j = b * LA_BN + kr;
+      const bool real = j <= p_last;
+      const int jj = real ? j : p_last;
+      const bf16* src = store + ((size_t)pages[jj / SB_PAGE_TOKENS] * SB_PAGE_TOKENS + jj % SB_PAGE_TOKENS) * Dk + c * 8;
+      cp_async16(dst + kr * ld + c * 8, src, real);
+    }
+  };
+  // the queries, and the first block of keys
+  for (int i = tid; i < LA_BM * chunks; i += 256) {
+    const int r = i / chunks, c = i - r * chunks;
+    const int tt = r / heads_per_block, hh = r - tt * heads_per_block;
+    const bool real = tt < n_tok && hh < n_heads;
+    const bf16* src = qa + ((size_t)(q_start + first_tok + (real ? tt : 0)) * heads + h0 + (real ? hh : 0)) * Dk + c * 8;
+    cp_async16(qs + r * ld + c * 8, src, real);
+  }
+  if (b_begin < b_end) load_keys(b_begin, 0);
+  cp_async_commit();
+
+  const int wr = warp & 3, wc = warp >> 2;
+  const int g = lane >> 2, tq = lane & 3;
+  const int c_half = (rank / 2 + 15) / 16 * 16;
+  const int col_lo = wc == 0 ? 0 : c_half, col_hi = wc == 0 ? c_half : rank;
+  const int n_pairs = (col_hi - col_lo) / 16;     // pairs of 8-column tiles this warp sums
+  int row_pos[2], row_lo[2];
+  bool row_ok[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = 16 * wr + g + 8 * i;
+    const int tt = r / heads_per_block, hh = r - tt * heads_per_block;
+    row_ok[i] = tt < n_tok && hh < n_heads;
+    row_pos[i] = p_first + tt;
+    row_lo[i] = window > 0 ? row_pos[i] - window + 1 : 0;
+  }
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  for (int b = b_begin; b < b_end; ++b) {
+    const int buf = (b - b_begin) & 1;
+    if (b + 1 < b_end) load_keys(b + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const bf16* kb = ks + (size_t)buf * LA_BN * ld;
+    float s[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int kk = 0; kk < Dk / 16; ++kk) {
+      unsigned a[4];
+      ldsm4(a, qs + (16 * wr + (lane & 15)) * ld + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        unsigned kf[4];
+        const int mi = lane >> 3;
+        ldsm4(kf, kb + (16 * np + (lane & 7) + (mi >> 1) * 8) * ld + kk * 16 + (mi & 1) * 8);
+        mma16816(s[2 * np], a, kf[0], kf[1]);
+        mma16816(s[2 * np + 1], a, kf[2], kf[3]);
+      }
+    }
+    // mask by each row's own position and window, running maximum and sum
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int j = b * LA_BN + n * 8 + 2 * tq + (e & 1);
+        const bool seen = row_ok[i] && j >= row_lo[i] && j <= row_pos[i];
+        s[n][e] = seen ? s[n][e] * scale : -INFINITY;
+        mx[i] = fmaxf(mx[i], s[n][e]);
+      }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+      const float m_new = fmaxf(m_run[i], mx[i]);
+      m_use[i] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[i] = expf(m_run[i] - m_use[i]);
+      m_run[i] = m_new;
+      l_run[i] *= alpha[i];
+    }
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s[n][e] = expf(s[n][e] - m_use[e >> 1]);
+        l_run[e >> 1] += s[n][e];
+      }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+      o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int k2 = 0; k2 < 2; ++k2) {
+      unsigned pa[4];
+      pa[0] = pack_bf16(s[2 * k2][0], s[2 * k2][1]);
+      pa[1] = pack_bf16(s[2 * k2][2], s[2 * k2][3]);
+      pa[2] = pack_bf16(s[2 * k2 + 1][0], s[2 * k2 + 1][1]);
+      pa[3] = pack_bf16(s[2 * k2 + 1][2], s[2 * k2 + 1][3]);
+#pragma unroll
+      for (int pr = 0; pr < NT / 2; ++pr) {
+        if (pr < n_pairs) {
+          unsigned vf[4];
+          const int mi = lane >> 3;
+          ldsm4_t(vf, kb + (16 * k2 + (lane & 7) + (mi & 1) * 8) * ld + col_lo + pr * 16 + (mi >> 1) * 8);
+          mma16816(o[2 * pr], pa, vf[0], vf[1]);
+          mma16816(o[2 * pr + 1], pa, vf[2], vf[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!row_ok[i]) continue;
+    const int r = 16 * wr + g + 8 * i;
+    const int tt = r / heads_per_block, hh = r - tt * heads_per_block;
+    const size_t grow = (size_t)(q_start + first_tok + tt) * heads + h0 + hh;
+    if (n_splits == 1) {
+      const float inv = 1.f / l_run[i];
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int col = col_lo + n * 8 + 2 * tq;
+        if (n < 2 * n_pairs)
+          *reinterpret_cast<unsigned*>(out + grow * rank + col) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+      }
+    } else {
+      float* pa = part_acc + ((size_t)split * n_rows_total + grow) * rank;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int col = col_lo + n * 8 + 2 * tq;
+        if (n < 2 * n_pairs) *reinterpret_cast<float2*>(pa + col) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+      }
+      if (wc == 0 && tq == 0) {
+        part_ml[((size_t)split * n_rows_total + grow) * 2] = m_run[i];
+        part_ml[((size_t)split * n_rows_total + grow) * 2 + 1] = l_run[i];
+      }
+    }
+  }
+}
+
+// out[row] = sum_s acc[s][row] exp(m_s - M) / sum_s l_s exp(m_s - M): a block a row.
+__global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                    bf16* __restrict__ out, int n_rows, int rank, int n_splits) {
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(part_acc);
+  SB_BEHIND_WAIT(part_ml);
+  const int row = blockIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[((size_t)s * n_rows + row) * 2]);
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float m = part_ml[((size_t)s * n_rows + row) * 2];
+    if (m != -INFINITY) L += part_ml[((size_t)s * n_rows + row) * 2 + 1] * expf(m - M);
+  }
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float m = part_ml[((size_t)s * n_rows + row) * 2];
+      if (m != -INFINITY) a += part_acc[((size_t)s * n_rows + row) * rank + c] * expf(m - M);
+    }
+    out[(size_t)row * rank + c] = from_f<bf16>(a / L);
+  }
+}
+
+extern "C" {
+
+// The bfloat16 attention on tensor cores.  seq_* describe the sequences of the step (slot, first packed
+// row, rows brought, length with them), tile_seq / tile_first list its tiles of 64 tokens.  part_acc
+// (float [n_splits, n_tokens * heads, rank]) and part_ml (float [n_splits, n_tokens * heads, 2]) are
+// scratch for n_splits > 1.  max_q_len: the most tokens a sequence brings, if the caller knows (it saves
+// launching blocks that would find nothing to do).  Returns -2 for sizes it does not take: rank and rot multiples of 16, rank up
+// to 512, rows of up to 640 entries.
+int sb_latent_attention_tc(const void* qa, void* out, float* part_acc, float* part_ml, const void* store,
+                           const int* block_table, int table_stride, const int* seq_slot, const int* seq_q_start,
+                           const int* seq_q_len, const int* seq_kv_len, const int* tile_seq, const int* tile_first,
+                           int n_tiles, int n_tokens, int heads, int rank, int rot, float scale, int window, int n_splits,
+                           int max_q_len, cudaStream_t s) {
+  if (n_tiles == 0 || n_tokens == 0) return 0;
+  if (rank % 16 || rot % 16 || rank < 16 || rank > 512 || rank + rot > 640 || n_splits < 1) return -2;
+  const int heads_per_block = heads < 64 ? heads : 64;
+  const int tokens_per_block = 64 / heads_per_block;
+  const int head_chunks = (heads + heads_per_block - 1) / heads_per_block;
+  // blocks a tile of 64 tokens is cut into; no sequence brings more than max_q_len (<= 0: unknown)
+  const int tile_tokens = max_q_len > 0 && max_q_len < 64 ? max_q_len : 64;
+  const int subs = (tile_tokens + tokens_per_block - 1) / tokens_per_block;
+  const int ld = rank + rot + 8;
+  const size_t smem = (size_t)(LA_BM + 2 * LA_BN) * ld * sizeof(bf16);
+  const dim3 grid(n_tiles * subs * head_chunks, n_splits);
+  const int c_half = (rank / 2 + 15) / 16 * 16;
+  const int nt = c_half / 8;
+#define GO(N)                                                                                                         \
+  {                                                                                                                   \
+    cudaFuncSetAttribute(latent_attention_tc_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    int rc = launch_dependent(latent_attention_tc_kernel<N>, grid, dim3(256), smem, s, (const bf16*)qa, (bf16*)out,   \
+                              part_acc, part_ml, (const bf16*)store, block_table, table_stride, seq_slot, seq_q_start, \
+                              seq_q_len, seq_kv_len, tile_seq, tile_first, heads, rank, rot, scale, window,           \
+                              tokens_per_block, heads_per_block, head_chunks, subs, n_tokens * heads);                \
+    if (rc != 0 || n_splits == 1) return rc;                                                                          \
+  }
+  if (nt <= 4) GO(4)
+  else if (nt <= 8) GO(8)
+  else if (nt <= 16) GO(16)
+  else GO(32)
+#undef GO
+  return launch_dependent(latent_merge_kernel, dim3(n_tokens * heads), dim3(128), 0, s, (const float*)part_acc,
+                          (const float*)part_ml, (bf16*)out, n_tokens * heads, rank, n_splits);
+}
+
+}  // extern "C"

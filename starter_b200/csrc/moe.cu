@@ -4,7 +4,7 @@
 //   route    z = W_r h + b in float; the `top` largest (the lower index first among equals); their
 //            weights are the softmax over those `top` logits alone.
 //   align    the (token, choice) pairs grouped by expert: every expert's pairs fill whole tiles of
-//            MOE_BM rows (padded with -1), `tile_expert` names each tile's expert, `n_tiles` counts them.
+//            rows (32, or 64 for the tensor-core tiles; padded with -1), `tile_expert` names each tile's expert, `n_tiles` counts them.
 //   up       per tile: g = min(gate(h), limit), u = clamp(up(h), -limit, limit),
 //            a = g * sigmoid(1.702 g) * (u + 1), for the tile's rows gathered from h.
 //   down     per tile: the expert's down projection of a, filed at the pair's own place.
@@ -77,7 +77,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
 
 // One block.  ids: [n_pairs]; sorted: [capacity] receives pair numbers or -1; tile_expert: [max_tiles].
 __global__ void moe_align_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ sorted,
-                                 int capacity, int* __restrict__ tile_expert, int* __restrict__ n_tiles) {
+                                 int capacity, int* __restrict__ tile_expert, int* __restrict__ n_tiles, int bm) {
   __shared__ int count[MOE_MAX_EXPERTS], offset[MOE_MAX_EXPERTS], total;
   pdl_trigger();
   pdl_wait();
@@ -90,9 +90,9 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e
     int off = 0, tiles = 0;
     for (int e = 0; e < experts; ++e) {
       offset[e] = off;
-      const int nt = (count[e] + MOE_BM - 1) / MOE_BM;
+      const int nt = (count[e] + bm - 1) / bm;
       for (int t = 0; t < nt; ++t) tile_expert[tiles++] = e;
-      off += nt * MOE_BM;
+      off += nt * bm;
       count[e] = 0;
     }
     n_tiles[0] = tiles;
@@ -195,20 +195,29 @@ moe_tile_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
   }
 }
 
-// The same tiles on the tensor cores (bfloat16, k and n_out multiples of 16): four warps, each a 16 x 32
-// (rows x outputs) piece of the 32 x 64 tile, wmma 16 x 16 x 16 with float accumulators; operands are
-// staged in shared memory, where the gathered rows become contiguous.
+// The same on the tensor cores (bfloat16, k a multiple of 16): tiles of 64 rows times 64 outputs, eight
+// warps (four groups of 16 rows times two halves of the outputs), wmma 16 x 16 x 16 with float
+// accumulators.  Rows (gathered through `sorted`) and weights arrive in k-slices of 32 through a ring of
+// three cp.async stages, so that the copies of the next two slices are in flight while one is multiplied.
+#define MOE_TC_BM 64
+__device__ __forceinline__ void moe_cp16(void* dst, const void* src, bool real) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int bytes = real ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
 template <bool UP>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
                    const int* __restrict__ sorted, const int* __restrict__ tile_expert,
                    const int* __restrict__ n_tiles, int k_dim, int n_out, int top, float limit) {
   using namespace nvcuda;
-  constexpr int BK = 64, LD = BK + 8;
-  __shared__ __align__(32) bf16 xs[MOE_BM][LD];
-  __shared__ __align__(32) bf16 ws[UP ? 2 : 1][MOE_BN][LD];
-  __shared__ __align__(32) float cs[UP ? 2 : 1][MOE_BM][MOE_BN + 4];
-  __shared__ int src[MOE_BM];
+  constexpr int BK = 32, LD = BK + 8, NW = UP ? 2 : 1, STAGES = 3, CLD = MOE_BN + 4;
+  extern __shared__ __align__(128) unsigned char moe_smem[];
+  bf16* xs = reinterpret_cast<bf16*>(moe_smem);                          // [STAGES][64][LD]
+  bf16* ws = xs + STAGES * MOE_TC_BM * LD;                               // [STAGES][NW][64][LD]
+  float* cs = reinterpret_cast<float*>(ws + STAGES * NW * MOE_BN * LD);  // [NW][64][CLD]
+  __shared__ int src[MOE_TC_BM];
   pdl_trigger();
   pdl_wait();
   SB_BEHIND_WAIT(x);
@@ -220,71 +229,77 @@ moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
   const int e = tile_expert[tile];
   const int n0 = blockIdx.y * MOE_BN;
   const int tid = threadIdx.x, warp = tid >> 5;
-  if (tid < MOE_BM) src[tid] = sorted[tile * MOE_BM + tid];
+  if (tid < MOE_TC_BM) src[tid] = sorted[tile * MOE_TC_BM + tid];
   __syncthreads();
-  const bf16* we = w + (size_t)e * (UP ? 2 : 1) * n_out * k_dim;
-  const int wm = warp >> 1, wn = warp & 1;
-  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[UP ? 2 : 1][2];
+  const bf16* we = w + (size_t)e * NW * n_out * k_dim;
+  const int lm = tid >> 2, lc = (tid & 3) * 8;          // this thread's row and 16-byte piece of every slice
+  const int pair = src[lm];
+  const bf16* x_row = x + (UP ? (size_t)(pair >= 0 ? pair / top : 0) : (size_t)tile * MOE_TC_BM + lm) * k_dim;
+  const bool w_in = n0 + lm < n_out;
+  const bf16* w_row = we + (size_t)(w_in ? n0 + lm : 0) * k_dim;
+  const int k_tiles = (k_dim + BK - 1) / BK;
+  auto load = [&](int kt, int st) {
+    const int kk = kt * BK + lc;
+    const bool in_k = kk < k_dim;
+    moe_cp16(xs + ((size_t)st * MOE_TC_BM + lm) * LD + lc, x_row + (in_k ? kk : 0), in_k && pair >= 0);
 #pragma unroll
-  for (int a = 0; a < (UP ? 2 : 1); ++a)
+    for (int a = 0; a < NW; ++a)
+      moe_cp16(ws + (((size_t)st * NW + a) * MOE_BN + lm) * LD + lc, w_row + (size_t)a * n_out * k_dim + (in_k ? kk : 0),
+               in_k && w_in);
+  };
+  const int wm = warp & 3, wn = warp >> 2;
+  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[NW][2];
+#pragma unroll
+  for (int a = 0; a < NW; ++a)
 #pragma unroll
     for (int j = 0; j < 2; ++j) wmma::fill_fragment(acc[a][j], 0.f);
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int k0 = 0; k0 < k_dim; k0 += BK) {
-    // 16-byte pieces: 8 bfloat16 (k_dim is a multiple of 16, so a piece is inside the row or outside it)
-    for (int i = tid; i < MOE_BM * (BK / 8); i += 128) {
-      const int m = i / (BK / 8), kk = (i % (BK / 8)) * 8;
-      const int pair = src[m];
-      uint4 v = zero;
-      if (pair >= 0 && k0 + kk < k_dim) {
-        const size_t row = UP ? (size_t)(pair / top) : (size_t)tile * MOE_BM + m;
-        v = *reinterpret_cast<const uint4*>(x + row * k_dim + k0 + kk);
-      }
-      *reinterpret_cast<uint4*>(&xs[m][kk]) = v;
-    }
-    for (int i = tid; i < (UP ? 2 : 1) * MOE_BN * (BK / 8); i += 128) {
-      const int a = i / (MOE_BN * (BK / 8)), rem = i % (MOE_BN * (BK / 8));
-      const int n = rem / (BK / 8), kk = (rem % (BK / 8)) * 8;
-      uint4 v = zero;
-      if (n0 + n < n_out && k0 + kk < k_dim)
-        v = *reinterpret_cast<const uint4*>(we + ((size_t)a * n_out + n0 + n) * k_dim + k0 + kk);
-      *reinterpret_cast<uint4*>(&ws[a][n][kk]) = v;
-    }
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (st < k_tiles) load(st, st);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  for (int kt = 0; kt < k_tiles; ++kt) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
     __syncthreads();
+    const int nk = kt + STAGES - 1;
+    if (nk < k_tiles) load(nk, nk % STAGES);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int st = kt % STAGES;
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fa;
-      wmma::load_matrix_sync(fa, &xs[wm * 16][kk], LD);
+      wmma::load_matrix_sync(fa, xs + ((size_t)st * MOE_TC_BM + wm * 16) * LD + kk, LD);
 #pragma unroll
-      for (int a = 0; a < (UP ? 2 : 1); ++a)
+      for (int a = 0; a < NW; ++a)
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fb;
-          wmma::load_matrix_sync(fb, &ws[a][wn * 32 + j * 16][kk], LD);
+          wmma::load_matrix_sync(fb, ws + (((size_t)st * NW + a) * MOE_BN + wn * 32 + j * 16) * LD + kk, LD);
           wmma::mma_sync(acc[a][j], fa, fb, acc[a][j]);
         }
     }
-    __syncthreads();
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
-  for (int a = 0; a < (UP ? 2 : 1); ++a)
+  for (int a = 0; a < NW; ++a)
 #pragma unroll
     for (int j = 0; j < 2; ++j)
-      wmma::store_matrix_sync(&cs[a][wm * 16][wn * 32 + j * 16], acc[a][j], MOE_BN + 4, wmma::mem_row_major);
+      wmma::store_matrix_sync(cs + ((size_t)a * MOE_TC_BM + wm * 16) * CLD + wn * 32 + j * 16, acc[a][j], CLD,
+                              wmma::mem_row_major);
   __syncthreads();
-  for (int i = tid; i < MOE_BM * MOE_BN; i += 128) {
+  for (int i = tid; i < MOE_TC_BM * MOE_BN; i += 256) {
     const int m = i / MOE_BN, nn = i % MOE_BN;
     const int n = n0 + nn;
-    const int pair = src[m];
+    const int row_pair = src[m];
     if (n >= n_out) continue;
     if (UP) {
-      float g = rnd<bf16>(cs[0][m][nn]), u = rnd<bf16>(cs[UP ? 1 : 0][m][nn]);
+      float g = rnd<bf16>(cs[(size_t)m * CLD + nn]), u = rnd<bf16>(cs[((size_t)(NW - 1) * MOE_TC_BM + m) * CLD + nn]);
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);
-      const float a = pair >= 0 ? g / (1.f + expf(-1.702f * g)) * (u + 1.f) : 0.f;
-      y[((size_t)tile * MOE_BM + m) * n_out + n] = from_f<bf16>(a);
-    } else if (pair >= 0) {
-      y[(size_t)pair * n_out + n] = from_f<bf16>(cs[0][m][nn]);
+      const float a = row_pair >= 0 ? g / (1.f + expf(-1.702f * g)) * (u + 1.f) : 0.f;
+      y[((size_t)tile * MOE_TC_BM + m) * n_out + n] = from_f<bf16>(a);
+    } else if (row_pair >= 0) {
+      y[(size_t)row_pair * n_out + n] = from_f<bf16>(cs[(size_t)m * CLD + nn]);
     }
   }
 }
@@ -307,7 +322,11 @@ __global__ void moe_combine_kernel(const T* __restrict__ down, const float* __re
 
 extern "C" {
 
-int sb_moe_tile_rows() { return MOE_BM; }
+// Rows of a tile for these operands: 64 when both products run on the tensor-core tiles (bfloat16, width and
+// inner size multiples of 16), else 32.
+int sb_moe_tile_rows(int dtype, int width, int inner) {
+  return dtype == 1 && width % 16 == 0 && inner % 16 == 0 ? MOE_TC_BM : MOE_BM;
+}
 int sb_moe_max_experts() { return MOE_MAX_EXPERTS; }
 int sb_moe_max_top() { return MOE_MAX_TOP; }
 
@@ -326,33 +345,39 @@ int sb_moe_route(int dtype, const void* h, const float* w, const float* b, int* 
 }
 
 int sb_moe_align(const int* ids, int n_pairs, int experts, int* sorted, int capacity, int* tile_expert, int* n_tiles,
-                 cudaStream_t s) {
-  if (experts < 1 || experts > MOE_MAX_EXPERTS) return -2;
+                 int tile_rows, cudaStream_t s) {
+  if (experts < 1 || experts > MOE_MAX_EXPERTS || tile_rows < 1) return -2;
   return launch_dependent(moe_align_kernel, dim3(1), dim3(256), 0, s, ids, n_pairs, experts, sorted, capacity,
-                          tile_expert, n_tiles);
+                          tile_expert, n_tiles, tile_rows);
 }
 
 // up != 0: x = h [n_tokens, k_dim], w = [experts, 2 * n_out, k_dim] (gate rows, then up rows), y =
 // [capacity, n_out] in the order of `sorted`.  up == 0: x = that y [capacity, k_dim], w = [experts,
 // n_out, k_dim], y = [n_pairs, n_out] by pair.
-int sb_moe_tiles(int dtype, int up, const void* x, const void* w, void* y, const int* sorted, const int* tile_expert,
-                 const int* n_tiles, int max_tiles, int k_dim, int n_out, int top, float limit, cudaStream_t s) {
+int sb_moe_tiles(int dtype, int up, int tile_rows, const void* x, const void* w, void* y, const int* sorted,
+                 const int* tile_expert, const int* n_tiles, int max_tiles, int k_dim, int n_out, int top, float limit,
+                 cudaStream_t s) {
   if (max_tiles == 0) return 0;
   const dim3 grid(max_tiles, (n_out + MOE_BN - 1) / MOE_BN);
+  if (tile_rows == MOE_TC_BM) {
+    if (dtype != 1 || k_dim % 16 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return -2;
+    const size_t smem = (size_t)3 * (1 + (up ? 2 : 1)) * 64 * 40 * sizeof(bf16) + (size_t)(up ? 2 : 1) * 64 * (MOE_BN + 4) * sizeof(float);
+    if (up) {
+      cudaFuncSetAttribute(moe_tile_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      return launch_dependent(moe_tile_tc_kernel<true>, grid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w,
+                              (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+    }
+    cudaFuncSetAttribute(moe_tile_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_dependent(moe_tile_tc_kernel<false>, grid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w,
+                            (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+  }
+  if (tile_rows != MOE_BM) return -2;
   if (dtype == 0) {
     if (up)
       return launch_dependent(moe_tile_kernel<float, true>, grid, dim3(256), 0, s, (const float*)x, (const float*)w,
                               (float*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
     return launch_dependent(moe_tile_kernel<float, false>, grid, dim3(256), 0, s, (const float*)x, (const float*)w,
                             (float*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
-  }
-  const bool tc = k_dim % 16 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0);
-  if (tc) {
-    if (up)
-      return launch_dependent(moe_tile_tc_kernel<true>, grid, dim3(128), 0, s, (const bf16*)x, (const bf16*)w,
-                              (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
-    return launch_dependent(moe_tile_tc_kernel<false>, grid, dim3(128), 0, s, (const bf16*)x, (const bf16*)w,
-                            (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
   }
   if (up)
     return launch_dependent(moe_tile_kernel<bf16, true>, grid, dim3(256), 0, s, (const bf16*)x, (const bf16*)w,

@@ -84,7 +84,8 @@ __global__ void residual_norm_kernel(float* __restrict__ x, const T* __restrict_
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f<T>(row[c] * inv * next_gain[c]);
 }
 
-// y[r, c] = act(x[r, c] + bias[c]); act 0: none, 1: relu, squared; 2: tanh.
+// y[r, c] = act(x[r, c] + bias[c]); act 0: none, 1: relu, squared; 2: tanh; 3: exp(-exp(.)), the decay
+// of a recurrence from its logarithm's logarithm.
 template <typename T>
 __global__ void bias_act_kernel(const T* __restrict__ x, const float* __restrict__ bias, T* __restrict__ y,
                                 int width, size_t total, int act) {
@@ -101,6 +102,8 @@ __global__ void bias_act_kernel(const T* __restrict__ x, const float* __restrict
       v = v * v;
     } else if (act == 2) {
       v = tanhf(v);
+    } else if (act == 3) {
+      v = expf(-expf(v));
     }
     y[i] = from_f<T>(v);
   }

@@ -1334,12 +1334,13 @@ def residual_norm(x, dtype, eps, pending=None, next_gain=None, rows=None):
 
 
 #: what ``bias_act`` can apply after the bias
-BIAS_ACTIVATIONS = {None: 0, "none": 0, "relu2": 1, "tanh": 2}
+BIAS_ACTIVATIONS = {None: 0, "none": 0, "relu2": 1, "tanh": 2, "decay": 3}
 
 
 def bias_act(x, bias=None, activation=None):
     """``act(x + bias)`` for ``x`` ``[T, N]`` and a float32 ``bias`` ``[N]`` (or None); ``activation``:
-    None, ``"relu2"`` (the square of relu) or ``"tanh"``.  The sum and the activation are float."""
+    None, ``"relu2"`` (the square of relu), ``"tanh"`` or ``"decay"`` (``exp(-exp(.))``: a recurrence's decay
+    factor from the logarithm of its negated logarithm).  The sum and the activation are float."""
     _need(x, "x", None, 2)
     if activation not in BIAS_ACTIVATIONS:
         raise KernelError(f"no activation {activation!r} here (known: relu2, tanh)")
@@ -1377,13 +1378,13 @@ def token_shift(h, state, mu, tok_slot):
     return out
 
 
-def wkv_scan(r, k, v, x_decay, w0, u, g, gain, state, h, seq_slot, seq_q_start, seq_q_len, heads, dim, eps):
+def wkv_scan(r, k, v, decay, u, g, gain, state, h, seq_slot, seq_q_start, seq_q_len, heads, dim, eps):
     """The recurrence ``o_t = (S + diag(u) k_t v_t^T)^T r_t``, ``S <- diag(w_t) S + k_t v_t^T`` with
-    ``w_t = exp(-exp(x_decay_t + w0))`` per head over the sequences of a step, followed by the head's
-    unit norm, ``gain`` and ``silu(g)``.
+    the decay factors ``w_t`` per head over the sequences of a step, followed by the head's unit norm,
+    ``gain`` and ``silu(g)``.
 
-    ``r, k, v, g`` ``[T, heads * dim]`` in the working type; ``x_decay`` float32 of that shape; ``w0``,
-    ``gain`` float32 ``[heads * dim]``; ``u`` float32 ``[heads, dim]``.  ``state`` float32 ``[slots, W +
+    ``r, k, v, g`` ``[T, heads * dim]`` in the working type; ``decay`` float32 of that shape (the factors
+    themselves, in (0, 1)); ``gain`` float32 ``[heads * dim]``; ``u`` float32 ``[heads, dim]``.  ``state`` float32 ``[slots, W +
     heads * dim * dim]``: each slot's last mixer input (``h``'s row, ``W`` floats, written here for the
     sequence's last token of this step) and its ``S``, read at the start and written at the end.
     Returns ``[T, heads * dim]`` in the working type."""
@@ -1396,8 +1397,7 @@ def wkv_scan(r, k, v, x_decay, w0, u, g, gain, state, h, seq_slot, seq_q_start, 
             raise KernelError(f"{name} has shape {tuple(t.shape)}, expected {(n_tokens, hd)}")
     if r.shape[1] != hd:
         raise KernelError(f"r has width {r.shape[1]}, expected {hd}")
-    _f32(x_decay, "x_decay", (n_tokens, hd))
-    _f32(w0, "w0", (hd,))
+    _f32(decay, "decay", (n_tokens, hd))
     _f32(gain, "gain", (hd,))
     _need(u, "u", torch.float32)
     if u.numel() != hd:
@@ -1410,13 +1410,16 @@ def wkv_scan(r, k, v, x_decay, w0, u, g, gain, state, h, seq_slot, seq_q_start, 
     for name, t in (("seq_slot", seq_slot), ("seq_q_start", seq_q_start), ("seq_q_len", seq_q_len)):
         _need(t, name, torch.int32, 1)
     out = torch.empty_like(r)
+    # many tokens of few sequences: scratch with which several blocks may share a head
+    o32 = torch.empty((n_tokens, hd), dtype=torch.float32, device=r.device) if n_tokens >= 4 * seq_slot.shape[0] else None
     rc = _lib("wkv").sb_wkv_scan(
-        _code(r.dtype), _ptr(r), _ptr(k), _ptr(v), _ptr(x_decay), _ptr(w0), _ptr(u), _ptr(g), _ptr(gain),
+        _code(r.dtype), _ptr(r), _ptr(k), _ptr(v), _ptr(decay), _ptr(u), _ptr(g), _ptr(gain),
         _ptr(state), ctypes.c_longlong(state.shape[1]), width, _ptr(h), width, _ptr(out), _ptr(seq_slot),
-        _ptr(seq_q_start), _ptr(seq_q_len), seq_slot.shape[0], heads, dim, ctypes.c_float(eps), _stream())
+        _ptr(seq_q_start), _ptr(seq_q_len), seq_slot.shape[0], heads, dim, ctypes.c_float(eps), _ptr(o32), n_tokens,
+        _stream())
     if rc == -2:
         raise KernelError(f"the recurrence kernel takes heads of 1 to {wkv_max_dim()} channels, not {dim}")
-    _check(rc, "wkv_scan")
+    _check(rc, "wkv_scan", 2 if o32 is not None and dim == 64 and seq_slot.shape[0] * heads <= 74 else 1)
     return out
 
 
@@ -1508,6 +1511,67 @@ def latent_attention(qa, store, block_table, tok_slot, tok_pos, heads, rank, rot
     return out
 
 
+def latent_tc_takes(dtype, rank: int, rot: int) -> bool:
+    """Whether the tensor-core latent attention takes these sizes: bfloat16, ``rank`` and ``rot`` multiples
+    of 16, ``rank`` up to 512 and rows of up to 640 entries."""
+    return dtype == torch.bfloat16 and rank % 16 == 0 and rot % 16 == 0 and 16 <= rank <= 512 and rank + rot <= 640
+
+
+def latent_attention_tc(qa, store, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len, tile_seq, tile_first,
+                        heads, rank, rot, scale, window=None, n_splits=1, max_q_len=0):
+    """``latent_attention`` on tensor cores (bfloat16): a block takes the heads of consecutive tokens of a
+    sequence (up to 64 query rows), which all score the same cache rows.  The ``seq_*`` arrays describe the
+    sequences of the step, ``tile_seq`` / ``tile_first`` list its tiles of 64 tokens.  ``n_splits`` > 1 deals
+    the keys of every block out to that many blocks, which a second kernel joins: for steps of few rows.
+    ``max_q_len``: the most tokens a sequence brings, if known (fewer idle blocks are launched)."""
+    _need(qa, "qa", torch.bfloat16, 3)
+    n_tokens = qa.shape[0]
+    if tuple(qa.shape[1:]) != (heads, rank + rot):
+        raise KernelError(f"qa has shape {tuple(qa.shape)}, expected [T, {heads}, {rank + rot}]")
+    if not latent_tc_takes(qa.dtype, rank, rot):
+        raise KernelError(f"the tensor-core latent attention takes rank and rot in multiples of 16, rank up to 512 "
+                          f"and rows up to 640; got {rank} and {rot}")
+    _need(store, "cache pages", qa.dtype, 4)
+    if tuple(store.shape[1:]) != (1, PAGE_TOKENS, rank + rot):
+        raise KernelError(f"cache pages have shape {tuple(store.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    for name, t in (("seq_slot", seq_slot), ("seq_q_start", seq_q_start), ("seq_q_len", seq_q_len),
+                    ("seq_kv_len", seq_kv_len), ("tile_seq", tile_seq), ("tile_first", tile_first)):
+        _need(t, name, torch.int32, 1)
+    out = torch.empty((n_tokens, heads, rank), dtype=qa.dtype, device=qa.device)
+    part_acc = part_ml = None
+    n_splits = max(1, int(n_splits))
+    if n_splits > 1:
+        part_acc = torch.empty((n_splits, n_tokens * heads, rank), dtype=torch.float32, device=qa.device)
+        part_ml = torch.empty((n_splits, n_tokens * heads, 2), dtype=torch.float32, device=qa.device)
+    rc = _lib("attention_latent").sb_latent_attention_tc(
+        _ptr(qa), _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(store), _ptr(block_table), block_table.shape[1],
+        _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(tile_seq), _ptr(tile_first),
+        tile_seq.shape[0], n_tokens, heads, rank, rot, ctypes.c_float(scale), int(window or 0), n_splits,
+        int(max_q_len), _stream())
+    _check(rc, "latent_attention_tc", 2 if n_splits > 1 else 1)
+    return out
+
+
+def latent_splits(rows: int, heads: int, window, kv_hint: int) -> int:
+    """Into how many parts the keys of a single-token step are cut: enough blocks to fill the SMs, no part
+    shorter than a block of 32 keys, at most 32."""
+    blocks = rows * -(-heads // 64)
+    keys = kv_hint if not window else min(window, max(kv_hint, 1))
+    return max(1, min(32, 148 // max(1, blocks), -(-max(keys, 1) // 32)))
+
+
+def latent_attention_step(qa, store, block_table, ctx, heads, rank, rot, scale, window=None):
+    """``latent_attention`` for the step ``ctx`` describes, on the kernel that fits its shape: tensor cores
+    for bfloat16 at sizes they take, the plain kernel otherwise (float32, other sizes)."""
+    if latent_tc_takes(qa.dtype, rank, rot):
+        splits = latent_splits(ctx.n_seqs, heads, window, ctx.max_kv_len) if ctx.max_q_len == 1 else 1
+        return latent_attention_tc(qa, store, block_table, ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len,
+                                   ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first, heads, rank, rot, scale, window,
+                                   splits, ctx.max_q_len)
+    return latent_attention(qa, store, block_table, ctx.tok_slot, ctx.tok_pos, heads, rank, rot, scale, window)
+
+
 # ---------------------------------------------------------------------------------------- routed experts
 
 def moe_limits():
@@ -1550,21 +1614,21 @@ def moe_experts(h, ids, weights, gate_up, down, limit):
     if tuple(gate_up.shape) != (experts, 2 * inner, width) or tuple(down.shape) != (experts, width, inner):
         raise KernelError(f"expert weights {tuple(gate_up.shape)} / {tuple(down.shape)} do not fit rows of {width}")
     lib = _lib("moe")
-    bm = lib.sb_moe_tile_rows()
+    bm = lib.sb_moe_tile_rows(_code(h.dtype), width, inner)     # 64: tensor-core tiles; 32: the plain ones
     n_pairs = n_tokens * top
     max_tiles = -(-n_pairs // bm) + min(experts, n_pairs)
     capacity = max_tiles * bm
     meta = torch.empty((capacity + max_tiles + 1,), dtype=torch.int32, device=h.device)
     sorted_pairs, tile_expert, n_tiles = meta[:capacity], meta[capacity:capacity + max_tiles], meta[capacity + max_tiles:]
     rc = lib.sb_moe_align(_ptr(ids), n_pairs, experts, _ptr(sorted_pairs), capacity, _ptr(tile_expert), _ptr(n_tiles),
-                          _stream())
+                          bm, _stream())
     _check(rc, "moe_align")
     act = torch.empty((capacity, inner), dtype=h.dtype, device=h.device)
-    rc = lib.sb_moe_tiles(_code(h.dtype), 1, _ptr(h), _ptr(gate_up), _ptr(act), _ptr(sorted_pairs), _ptr(tile_expert),
+    rc = lib.sb_moe_tiles(_code(h.dtype), 1, bm, _ptr(h), _ptr(gate_up), _ptr(act), _ptr(sorted_pairs), _ptr(tile_expert),
                           _ptr(n_tiles), max_tiles, width, inner, top, ctypes.c_float(limit), _stream())
     _check(rc, "moe_up")
     per_pair = torch.empty((n_pairs, width), dtype=h.dtype, device=h.device)
-    rc = lib.sb_moe_tiles(_code(h.dtype), 0, _ptr(act), _ptr(down), _ptr(per_pair), _ptr(sorted_pairs),
+    rc = lib.sb_moe_tiles(_code(h.dtype), 0, bm, _ptr(act), _ptr(down), _ptr(per_pair), _ptr(sorted_pairs),
                           _ptr(tile_expert), _ptr(n_tiles), max_tiles, inner, width, top, ctypes.c_float(limit), _stream())
     _check(rc, "moe_down")
     out = torch.empty_like(h)

@@ -91,8 +91,8 @@ class LatentAttention(Part):
         torch.bmm(q3[:, :, : s.head_dim].transpose(0, 1), self.uk, out=qa[:, :, : s.kv_rank].transpose(0, 1))
         ops.latent_rotate_q(q, qa, cos, sin, ctx.tok_pos, s.num_heads, s.head_dim, s.rot_dim, s.position.dims,
                             s.kv_rank)
-        summed = ops.latent_attention(qa, store, cache.block_table, ctx.tok_slot, ctx.tok_pos, s.num_heads,
-                                      s.kv_rank, s.rot_dim, s.scale, s.window)
+        summed = ops.latent_attention_step(qa, store, cache.block_table, ctx, s.num_heads, s.kv_rank, s.rot_dim,
+                                           s.scale, s.window)
         a = torch.empty((n, s.num_heads, s.value_dim), dtype=q.dtype, device=q.device)
         torch.bmm(summed.transpose(0, 1), self.uv, out=a.transpose(0, 1))
         return ops.linear(a.view(n, s.num_heads * s.value_dim), self.o, status=ctx.status)

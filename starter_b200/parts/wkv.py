@@ -4,7 +4,7 @@ RWKV family), with its state in the cache's per-sequence slots.
 One step of it: ``ops.token_shift`` forms the five mixes of each token's input with its predecessor's
 (the predecessor of a portion's first token is what the sequence left in its slot); receptance, key,
 value and gate are projections of their mixes; the decay goes through two small matrices with a tanh
-between them and comes back in float32; ``ops.wkv_scan`` walks the tokens each sequence brings, from the
+between them, comes back in float32 and becomes ``exp(-exp(. + w0))`` there; ``ops.wkv_scan`` walks the tokens each sequence brings, from the
 state in its slot and back into it, and applies the head norm, the gain and the gate; the output
 projection follows.  A whole prompt, a later portion and a single token are the same code, and a step
 captured in a CUDA graph too: everything the kernels need is in the step's device arrays.
@@ -71,8 +71,8 @@ class WkvMixer(Part):
         v = ops.linear(mixes[2], self.v, status=ctx.status)
         g = ops.linear(mixes[3], self.g, status=ctx.status)
         inner = ops.bias_act(ops.linear(mixes[4], self.w1, status=ctx.status), None, "tanh")
-        x_decay = ops.linear(inner, self.w2, out_float=True, status=ctx.status)
-        o = ops.wkv_scan(r, k, v, x_decay, self.w0, self.u, g, self.gain, state, x, ctx.seq_slot,
+        decay = ops.bias_act(ops.linear(inner, self.w2, out_float=True, status=ctx.status), self.w0, "decay")
+        o = ops.wkv_scan(r, k, v, decay, self.u, g, self.gain, state, x, ctx.seq_slot,
                          ctx.seq_q_start, ctx.seq_q_len, s.num_heads, s.head_dim, s.norm_eps)
         return ops.linear(o, self.o, status=ctx.status)
 

@@ -189,7 +189,7 @@ def test_recurrence_alone_whole_in_portions_and_token_by_token(heads, dim, dtype
     r, k, v, gate, x_decay, w0, u, gain = wkv_inputs(heads, dim, lengths, 7)
     rd, kd, vd, gd = (dev(a, t) for a in (r, k, v, gate))
     r, k, v, gate = (a.double().cpu() for a in (rd, kd, vd, gd))
-    xdd, w0d, ud, gaind = dev(x_decay), dev(w0), dev(u), dev(gain)
+    xdd, ud, gaind = ops.bias_act(dev(x_decay), dev(w0), "decay"), dev(u), dev(gain)
     h = dev(torch.randn(sum(lengths), width, generator=torch.Generator().manual_seed(2)), t)
     starts = [0, lengths[0], lengths[0] + lengths[1]]
     want = torch.cat([plain_wkv(*(a[s:s + n] for a in (r, k, v, gate, x_decay)), w0, u, gain, heads, dim, 1e-5)
@@ -198,7 +198,7 @@ def test_recurrence_alone_whole_in_portions_and_token_by_token(heads, dim, dtype
     slots = [4, 1, 2]
     state[slots] = 0.0
     ints = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")  # noqa: E731
-    out = ops.wkv_scan(rd, kd, vd, xdd, w0d, ud, gd, gaind, state, h, ints(slots), ints(starts), ints(lengths),
+    out = ops.wkv_scan(rd, kd, vd, xdd, ud, gd, gaind, state, h, ints(slots), ints(starts), ints(lengths),
                        heads, dim, 1e-5)
     close(out, want, dtype, f"whole, heads {heads} x {dim}", fp32=5e-5)
     for i, slot in enumerate(slots):       # the last mixer input of every sequence is in its slot
@@ -215,7 +215,7 @@ def test_recurrence_alone_whole_in_portions_and_token_by_token(heads, dim, dtype
         idx = torch.cat([torch.arange(starts[i] + done[i], starts[i] + done[i] + cuts[i][step]) for i in live]).cuda()
         sizes = [cuts[i][step] for i in live]
         offs = [sum(sizes[:j]) for j in range(len(live))]
-        out = ops.wkv_scan(rd[idx].contiguous(), kd[idx].contiguous(), vd[idx].contiguous(), xdd[idx].contiguous(), w0d,
+        out = ops.wkv_scan(rd[idx].contiguous(), kd[idx].contiguous(), vd[idx].contiguous(), xdd[idx].contiguous(),
                            ud, gd[idx].contiguous(), gaind, state, h[idx].contiguous(), ints([slots[i] for i in live]),
                            ints(offs), ints(sizes), heads, dim, 1e-5)
         for j, i in enumerate(live):
@@ -254,7 +254,7 @@ def test_recurrence_keeps_what_a_far_token_wrote(dtype):
     parts = []
     for lo, hi in ((0, 250), (250, 330)):
         parts.append(ops.wkv_scan(rd[lo:hi].contiguous(), kd[lo:hi].contiguous(), vd[lo:hi].contiguous(),
-                                  dev(x_decay[lo:hi]), dev(w0), dev(u), gd[lo:hi].contiguous(), dev(gain), state,
+                                  ops.bias_act(dev(x_decay[lo:hi]), dev(w0), "decay"), dev(u), gd[lo:hi].contiguous(), dev(gain), state,
                                   h[lo:hi].contiguous(), ints([1]), ints([0]), ints([hi - lo]), 1, dim, 1e-5))
     close(torch.cat(parts), want, dtype, "a far token in a slow channel", fp32=5e-5)
 
@@ -302,7 +302,8 @@ def plain_latent(qa, rows, rank, scale, window):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, rank, rot, window", [(3, 32, 8, 10), (1, 48, 16, 3), (4, 64, 32, 65), (4, 64, 32, 64),
-                                                      (2, 20, 6, 0), (5, 16, 4, 500), (2, 512, 64, 100), (3, 24, 8, 1)])
+                                                      (2, 20, 6, 0), (5, 16, 4, 500), (2, 512, 64, 100), (3, 24, 8, 1),
+                                                      (5, 96, 16, 0), (70, 32, 16, 40), (16, 128, 32, 33)])
 def test_latent_attention_alone_with_one_key_that_stands_out(heads, rank, rot, window, dtype):
     """Queries late in a sequence of 200 (pages 0 to 3, scattered) score one key far above the rest: the
     key just inside the window, just outside it, on either side of a page border, the query's own place
@@ -341,6 +342,21 @@ def test_latent_attention_alone_with_one_key_that_stands_out(heads, rank, rot, w
     out = ops.latent_attention(qd[tail].contiguous(), store, table, slot[tail].contiguous(), pos[tail].contiguous(),
                                heads, rank, rot, 0.11, window or None)
     close(out, want[160:], dtype, f"window {window}, single tokens", bf16=1.5e-2)
+    if not ops.latent_tc_takes(t, rank, rot):
+        return
+    # the tensor-core kernel: the whole sequence as one step (four tiles of 64 tokens), then its last 40
+    # tokens as a later portion, then the last token alone with its keys cut into 1, 3 and 7 parts
+    ints = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")  # noqa: E731
+    out = ops.latent_attention_tc(qd, store, table, ints([1]), ints([0]), ints([n]), ints([n]), ints([0, 0, 0, 0]),
+                                  ints([128, 0, 192, 64]), heads, rank, rot, 0.11, window or None)
+    close(out, want, dtype, f"tensor cores, window {window}", bf16=1.5e-2)
+    out = ops.latent_attention_tc(qd[tail].contiguous(), store, table, ints([1]), ints([0]), ints([40]), ints([n]),
+                                  ints([0]), ints([0]), heads, rank, rot, 0.11, window or None)
+    close(out, want[160:], dtype, f"tensor cores, window {window}, a portion", bf16=1.5e-2)
+    for parts in (1, 3, 7):
+        out = ops.latent_attention_tc(qd[199:].contiguous(), store, table, ints([1]), ints([0]), ints([1]), ints([n]),
+                                      ints([0]), ints([0]), heads, rank, rot, 0.11, window or None, n_splits=parts)
+        close(out, want[199:], dtype, f"tensor cores, window {window}, one token in {parts} parts", bf16=1.5e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
