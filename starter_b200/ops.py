@@ -277,8 +277,24 @@ def tensor_core_ok(x, weight, gated, n_out) -> bool:
     return True
 
 
-@functools.lru_cache(maxsize=4096)     # asked once per launch, with the same few shapes step after step
+def whole_splits(k_blocks: int, splits: int) -> int:
+    """The largest number of parts up to ``splits`` that leaves no part without a k-block: the kernel gives
+    every part ``ceil(k_blocks / parts)`` blocks, so with 30 blocks in 7 parts the seventh would get none
+    and its accumulator would never be committed."""
+    splits = max(1, min(splits, k_blocks))
+    while splits > 1 and -(-k_blocks // splits) * (splits - 1) >= k_blocks:
+        splits -= 1
+    return splits
+
+
 def gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
+    """``_gemm_plan`` with the parts of the k range cut down to a number that leaves none empty."""
+    bm, splits, stages = _gemm_plan(rows, n_out, k_dim, gated)
+    return bm, whole_splits(-(-k_dim // 64), splits), stages
+
+
+@functools.lru_cache(maxsize=4096)     # asked once per launch, with the same few shapes step after step
+def _gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
     """``(bm, splits, stages)``: activation rows per tile; how many CTAs (one cluster) share a tile's
     k range; how deep the ring of shared-memory stages is.
 
@@ -354,7 +370,7 @@ def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=
                           f"widths in steps of 64; got k = {k_dim}, n = {n_out}")
     plan = gemm_plan(rows, n_out, k_dim, gated)
     bm = bm or plan[0]
-    splits = splits or plan[1]
+    splits = whole_splits(-(-k_dim // 64), splits or plan[1])
     stages = stages or max(plan[2], -(-bm * 512 // (16384 + bm * 128)))
     stages = min(stages, (226 * 1024) // (16384 + bm * 128))     # a tile height other than the plan's
     out = torch.empty((rows, n_out), dtype=torch.float32 if out_float else torch.bfloat16, device=x.device)
