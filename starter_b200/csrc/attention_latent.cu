@@ -304,7 +304,8 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
   const int tile = blockIdx.x / per_tile, rem = blockIdx.x % per_tile;
   const int sub = rem / head_chunks, hc = rem % head_chunks;
   const int split = blockIdx.y, n_splits = gridDim.y;
-  pdl_trigger();
+  // (launch_dependents comes at this kernel's end, not its start: it runs in several waves of large blocks,
+  // and a successor that starts early would only sit on the SMs its later waves need)
   pdl_wait();
   SB_BEHIND_WAIT(qa); SB_BEHIND_WAIT(store); SB_BEHIND_WAIT(block_table);
   SB_BEHIND_WAIT(seq_slot); SB_BEHIND_WAIT(seq_q_start); SB_BEHIND_WAIT(seq_q_len); SB_BEHIND_WAIT(seq_kv_len);
@@ -446,6 +447,7 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
     __syncthreads();
   }
   cp_async_wait<0>();
+  pdl_trigger();
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);

@@ -119,7 +119,8 @@ moe_tile_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
   __shared__ float xs[MOE_BM][MOE_BK + 1];
   __shared__ float ws[UP ? 2 : 1][MOE_BN][MOE_BK + 1];
   __shared__ int src[MOE_BM];
-  pdl_trigger();
+  // (launch_dependents comes at this kernel's end, not its start: it runs in several waves of large blocks,
+  // and a successor that starts early would only sit on the SMs its later waves need)
   pdl_wait();
   SB_BEHIND_WAIT(x);
   SB_BEHIND_WAIT(sorted);
@@ -218,7 +219,8 @@ moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
   bf16* ws = xs + STAGES * MOE_TC_BM * LD;                               // [STAGES][NW][64][LD]
   float* cs = reinterpret_cast<float*>(ws + STAGES * NW * MOE_BN * LD);  // [NW][64][CLD]
   __shared__ int src[MOE_TC_BM];
-  pdl_trigger();
+  // (launch_dependents comes at this kernel's end, not its start: it runs in several waves of large blocks,
+  // and a successor that starts early would only sit on the SMs its later waves need)
   pdl_wait();
   SB_BEHIND_WAIT(x);
   SB_BEHIND_WAIT(sorted);
@@ -280,6 +282,7 @@ moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+  pdl_trigger();
 #pragma unroll
   for (int a = 0; a < NW; ++a)
 #pragma unroll

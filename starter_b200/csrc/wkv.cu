@@ -81,7 +81,8 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
   const int row4 = 4 * D;
   const int e_tt0 = tid / row4, e_col0 = tid - e_tt0 * row4;
   const int e_dtt = nt / row4, e_dcol = nt - e_dtt * row4;
-  pdl_trigger();
+  // (launch_dependents comes at this kernel's end, not its start: it runs in several waves of large blocks,
+  // and a successor that starts early would only sit on the SMs its later waves need)
   pdl_wait();
   SB_BEHIND_WAIT(r); SB_BEHIND_WAIT(k); SB_BEHIND_WAIT(v); SB_BEHIND_WAIT(decay); SB_BEHIND_WAIT(g);
   SB_BEHIND_WAIT(state); SB_BEHIND_WAIT(h);
@@ -259,6 +260,7 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
     if (c + 1 < n_chunks) stash(buf ^ 1);
     __syncthreads();
   }
+  pdl_trigger();
 #pragma unroll
   for (int m = 0; m < KPT; ++m)
     if (live && i0 + m < D) S_mem[i0 + m] = S[m];
