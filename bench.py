@@ -705,8 +705,9 @@ def kesedra_compare(args) -> int:
         return {k: {a: round(b, 4 if "frac" in a else 1) for a, b in v.items()} for k, v in out.items()}
 
     results = {}
-    # the 2048 size alone by default: at 2560 with 8 layers a prompt step of this design once failed to return
-    # within ten minutes, for a reason that was not found; the larger sizes run when they are named
+    # the 2048 size alone by default: at 2560 with 8 layers a prompt step of this design failed to return while
+    # its kernels still released their successors early; the larger sizes have not been timed since and run
+    # when they are named
     for size_name in (args.design_sizes.split(",") if args.design_sizes else ["2048"]):
         size = DESIGN_SIZES[size_name]
         row = {"layers": layers}

@@ -28,8 +28,7 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, int proj_width
                                       const int* __restrict__ block_table, int table_stride, T* __restrict__ store,
                                       T* __restrict__ cq, int q_rank, int rank, int rot, int rot_dims, int write) {
   __shared__ float scratch[33];
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(proj);
   SB_BEHIND_WAIT(tok_pos);
   SB_BEHIND_WAIT(tok_slot);
@@ -77,8 +76,7 @@ __global__ void latent_rotate_q_kernel(const T* __restrict__ q, T* __restrict__ 
                                        const float* __restrict__ sin_t, int table_width,
                                        const int* __restrict__ tok_pos, int heads, int dim, int rot, int rot_dims,
                                        int rank) {
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(q);
   SB_BEHIND_WAIT(tok_pos);
   const int row = blockIdx.x;
@@ -106,8 +104,7 @@ __global__ void latent_attention_kernel(const T* __restrict__ qa, T* __restrict_
                                         const int* __restrict__ block_table, int table_stride,
                                         const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
                                         int n_tokens, int heads, int rank, int rot, float scale, int window) {
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(qa);
   SB_BEHIND_WAIT(store);
   SB_BEHIND_WAIT(tok_slot);
@@ -485,8 +482,7 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
 // out[row] = sum_s acc[s][row] exp(m_s - M) / sum_s l_s exp(m_s - M): a block a row.
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int n_rows, int rank, int n_splits) {
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(part_acc);
   SB_BEHIND_WAIT(part_ml);
   const int row = blockIdx.x;

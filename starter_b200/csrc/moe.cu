@@ -27,8 +27,7 @@ template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w, const float* __restrict__ b,
                                  int* __restrict__ ids, float* __restrict__ weights, int width, int experts, int top) {
   extern __shared__ float z[];
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(h);
   const int row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -79,8 +78,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
 __global__ void moe_align_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ sorted,
                                  int capacity, int* __restrict__ tile_expert, int* __restrict__ n_tiles, int bm) {
   __shared__ int count[MOE_MAX_EXPERTS], offset[MOE_MAX_EXPERTS], total;
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(ids);
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
   __syncthreads();
@@ -310,8 +308,7 @@ moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ down, const float* __restrict__ weights, T* __restrict__ out,
                                    int width, int top) {
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(down);
   SB_BEHIND_WAIT(weights);
   const int row = blockIdx.x;

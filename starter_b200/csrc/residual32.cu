@@ -20,8 +20,7 @@
 template <typename T>
 __global__ void embed32_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                float* __restrict__ out, int hidden, int vocab, float scale, int* status) {
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(tokens);
   const int row = blockIdx.x;
   int tok = tokens[row];
@@ -43,8 +42,7 @@ __global__ void residual_norm_kernel(float* __restrict__ x, const T* __restrict_
                                      const int* __restrict__ rows, int hidden, float eps_post, float eps) {
   extern __shared__ float row[];
   __shared__ float scratch[33];
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(y);
   SB_BEHIND_WAIT(rows);
   SB_BEHIND_WAIT(x);
@@ -89,8 +87,7 @@ __global__ void residual_norm_kernel(float* __restrict__ x, const T* __restrict_
 template <typename T>
 __global__ void bias_act_kernel(const T* __restrict__ x, const float* __restrict__ bias, T* __restrict__ y,
                                 int width, size_t total, int act) {
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(x);
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;

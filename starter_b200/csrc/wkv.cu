@@ -28,8 +28,7 @@ template <typename T>
 __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restrict__ state, size_t state_stride,
                                    const float* __restrict__ mu, T* __restrict__ out,
                                    const int* __restrict__ tok_slot, int n_tokens, int width, int n_mix) {
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(h);
   SB_BEHIND_WAIT(state);
   SB_BEHIND_WAIT(tok_slot);
@@ -275,8 +274,7 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
 template <typename T>
 __global__ void wkv_finish_kernel(const float* __restrict__ o32, const T* __restrict__ g, const float* __restrict__ gain,
                                   T* __restrict__ out, int n_tokens, int heads, int D, float eps) {
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(o32);
   SB_BEHIND_WAIT(g);
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
